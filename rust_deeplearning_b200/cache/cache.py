@@ -25,7 +25,7 @@ every row they touch holds finite numbers.)
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, NamedTuple, Optional, Sequence, Tuple
+from typing import Dict, List, NamedTuple, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
@@ -58,10 +58,18 @@ class StateRequirement:
 
 
 class RunNeeds(NamedTuple):
-    """What one schedule entry needs of the cache."""
+    """What one schedule entry needs of the cache.  `state`: one StateRequirement, or a tuple of them for a run
+    that keeps several tensors per sequence (a recurrent state, the last inputs of a convolution, the row before
+    a step's first row); `RunCache.state` is then a tuple of tensors in the same order."""
     kv: Optional[KVRequirement] = None
-    state: Optional[StateRequirement] = None
+    state: Union[None, StateRequirement, Tuple[StateRequirement, ...]] = None
     reads_cache_of: Optional[int] = None   # schedule entry whose keys and values it reads
+
+
+def _state_list(state) -> Tuple[StateRequirement, ...]:
+    if state is None:
+        return ()
+    return tuple(state) if isinstance(state, (tuple, list)) else (state,)
 
 
 class PagePool:
@@ -165,7 +173,7 @@ class RunCache(NamedTuple):
     v: Optional[torch.Tensor]       # [pages, kv_heads, page_size, value_dim or head_dim]
     page_size: int
     ring_pages: int
-    state: Optional[torch.Tensor]   # [max_seqs, *shape], indexed by slot
+    state: Union[None, torch.Tensor, Tuple[torch.Tensor, ...]]   # [max_seqs, *shape], indexed by slot (a tuple for several requirements)
     owns_kv: bool                   # False: the run reads another run's keys and values
     is_ring: bool = False           # the group keeps a window of keys: a position's row is reused later
 
@@ -191,6 +199,7 @@ class Cache:
 
         kv_by_req: Dict[KVRequirement, List[int]] = {}
         state_by_req: Dict[StateRequirement, List[int]] = {}
+        state_place: Dict[Tuple[int, int], Tuple[StateRequirement, int]] = {}
         for e, n in enumerate(self.needs):
             if n.reads_cache_of is not None:
                 src = self.needs[n.reads_cache_of]
@@ -201,14 +210,17 @@ class Cache:
                     raise CacheError(f"run {e} cannot read the cache of run {n.reads_cache_of}: head layout differs")
             elif n.kv is not None:
                 kv_by_req.setdefault(n.kv, []).append(e)
-            if n.state is not None:
-                state_by_req.setdefault(n.state, []).append(e)
+            for j, req in enumerate(_state_list(n.state)):
+                members = state_by_req.setdefault(req, [])
+                state_place[(e, j)] = (req, len(members))      # a run with two equal requirements is listed twice
+                members.append(e)
         self.kv_groups = [KVGroup(req, runs, max_tokens=self.max_tokens, max_seqs=self.max_seqs,
                                   max_context=self.max_context, page_size=page_size, dtype=dtype, device=device,
                                   allocate=allocate) for req, runs in kv_by_req.items()]
         self.state_groups = [StateGroup(req, runs, self.max_seqs, device, allocate) for req, runs in state_by_req.items()]
         self._kv_of_run = {e: (gi, g.runs.index(e)) for gi, g in enumerate(self.kv_groups) for e in g.runs}
-        self._state_of_run = {e: (gi, g.runs.index(e)) for gi, g in enumerate(self.state_groups) for e in g.runs}
+        group_of = {g.requirement: gi for gi, g in enumerate(self.state_groups)}
+        self._state_of_run = {key: (group_of[req], idx) for key, (req, idx) in state_place.items()}     # (run, j) -> (group, row)
 
         self._free_slots = list(range(self.max_seqs - 1, -1, -1))
         self._live = [False] * self.max_seqs
@@ -289,11 +301,12 @@ class Cache:
             k = g.k[idx] if g.k is not None else None
             v = g.v[idx] if g.v is not None else None
             ring, is_ring = g.ring_pages, g.is_ring
-        state = None
-        if run in self._state_of_run:
-            gi, idx = self._state_of_run[run]
+        states = []
+        for j in range(len(_state_list(n.state))):
+            gi, idx = self._state_of_run[(run, j)]
             data = self.state_groups[gi].data
-            state = data[idx] if data is not None else None
+            states.append(data[idx] if data is not None else None)
+        state = tuple(states) if isinstance(n.state, (tuple, list)) else (states[0] if states else None)
         return RunCache(kv_group, k, v, page_size, ring, state, n.reads_cache_of is None, is_ring)
 
     def nbytes(self):

@@ -53,3 +53,15 @@ __device__ __forceinline__ float rdl_gated_fast(float g, float u, int act, float
     }
     return rdl_activation_fast(g, act) * u;
 }
+
+// Element-wise activations of a product that is not gated (codes from 16 on, so that a plain product called with the
+// gated forms' default code 0 stays plain): relu2(x) = max(x, 0)^2, silu.
+static inline bool rdl_unary_known(int act) { return act == RDL_UNARY_RELU2 || act == RDL_UNARY_SILU; }
+__device__ __forceinline__ float rdl_unary(float x, int act) {
+    if (act == RDL_UNARY_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+    return x / (1.0f + expf(-x));
+}
+__device__ __forceinline__ float rdl_unary_fast(float x, int act) {
+    if (act == RDL_UNARY_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+    return __fdividef(x, 1.0f + __expf(fminf(-x, 80.0f)));
+}

@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 15
+#define RDL_ABI_VERSION 16
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -67,6 +67,9 @@ typedef struct {
     // optional: one float per query head, a logit without key or value that joins the softmax's denominator
     // (exp(sinks[h]) counts once; it is neither scaled nor capped); NULL: none
     const float* sinks;
+    // optional: one float per query head; the weight of a visible key is then sigmoid(score + sigmoid_bias[h]) and
+    // the weights are not normalised over the keys (no softmax, no denominator, no sinks); NULL: softmax
+    const float* sigmoid_bias;
     // filled in by the launcher: clock cycles after which a wait is given up, and the test's extra bytes
     long long wait_cycles; int test_extra_tx;
 } AttentionArgs;
@@ -129,8 +132,63 @@ int rdl_gate_mul(void* out, long long out_stride, const void* x, long long x_str
                  int dtype, int gate_act, int n_rows, int width, void* stream);
 // Float rows x [rows][groups * group] normed group by group (v / sqrt(mean(v^2) + eps), times w[column] if w is given),
 // times gate_act(g[t, column]) if g is given, written in out_dtype.
+// gate_first: the gate multiplies x before the norm (the root mean square is that of the gated values).
 int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int n_rows, int groups, int group, const void* w,
-                        int w_dtype, float eps, const void* g, long long g_stride, int g_dtype, int gate_act, void* stream);
+                        int w_dtype, float eps, const void* g, long long g_stride, int g_dtype, int gate_act, int gate_first,
+                        void* stream);
+
+// ---- rows that look back along their sequence (csrc/seq_state.cu) ----
+// normed[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w and mixed[t] = normed[t] + (normed[t - 1] - normed[t]) * shift, element by
+// element, in float; the row before a sequence's first row of the step is state[slot] (zeros at position 0), and
+// state[slot] is left holding the sequence's last normed row.  x float [rows][width]; state float [slots][width].
+int rdl_norm_shift(const float* x, const void* w, int w_dtype, float eps, const void* shift, int shift_dtype, float* state,
+                   const int* tok_seq, const int* tok_pos, const int* seq_start, const int* slots, void* normed, void* mixed,
+                   int out_dtype, int n_rows, int width, void* stream);
+// out[t, c] = act(bias[c] + sum_j w[c, j] in[t - (taps - 1 - j), c]) along each sequence (zeros before its start), the
+// sum in float; inputs of earlier steps are state[slot][taps - 1][channels] (float), which is left holding the
+// sequence's last taps - 1 inputs.  in: rows with a stride of their own; out dense [rows][channels]; bias optional.
+int rdl_short_conv(const void* in, long long in_stride, int dtype, int channels, int taps, const void* w, int w_dtype,
+                   const void* bias, int silu, float* state, const int* tok_seq, const int* tok_pos, const int* seq_start,
+                   const int* slots, void* out, int n_rows, void* stream);
+// res[t, i] += sigmoid(gates[t, i] + bias_a[i]) a[t, i] + sigmoid(gates[t, width + i] + bias_b[i]) (b1[t, i] + b2[t, i]), in float;
+// b1 NULL: the first term only; b2 optional
+int rdl_gated_residual_add(float* res, const void* gates, long long gates_stride, const void* bias_a, const void* bias_b,
+                           int bias_dtype, const void* a, const void* b1, const void* b2, int dtype, int n_rows, int width,
+                           void* stream);
+#define RDL_UNARY_RELU2 16     // max(x, 0)^2
+#define RDL_UNARY_SILU 17
+int rdl_activation_inplace(void* x, int dtype, long long total, int act, void* stream);
+
+// ---- recurrences whose decay depends on the token (csrc/recurrence.cu) ----
+#define RDL_REC_SSM 0
+#define RDL_REC_DELTA 1
+typedef struct {
+    int dtype;                                  // of the rows
+    int mode;
+    int n_tokens, n_seqs, n_heads, n_key_heads, dim, vdim;
+    const void* rows; long long row_stride;     // v (state space: x) of every head from v_col; state space: B from k_col, C from q_col
+    int q_col, k_col, v_col;
+    // state space: the raw step sizes [tokens][heads] with a stride of their own, and float parameters per head
+    const void* dt_rows; long long dt_stride;
+    const float* dt_bias; const float* a_log; const float* d_skip;
+    // delta rule: float [tokens][key heads * dim], [tokens][heads * dim], [tokens][heads]
+    const float* q_f; const float* k_f; const float* g_f; const float* beta_f;
+    const int* tok_pos; const int* seq_start; const int* slots;
+    float* state;                               // [slots][heads][dim][vdim]
+    float* out;                                 // [tokens][heads * vdim]
+} RecurrenceArgs;
+int rdl_recurrence_scan(const RecurrenceArgs* a, void* stream);
+typedef struct {
+    int dtype, bias_dtype;
+    int n_tokens, n_heads, n_key_heads, dim;
+    const void* rows; long long row_stride; int q_col, k_col;       // q and k of the key heads
+    const void* decay_rows; long long decay_stride;                 // raw decay logits [tokens][heads * dim]
+    const void* beta_rows; long long beta_stride;                   // raw beta logits [tokens][heads]
+    const void* dt_bias; const float* a_log;                        // [heads * dim] (bias_dtype), [heads]
+    float q_scale, unit_eps;
+    float* q_f; float* k_f; float* g_f; float* beta_f;
+} DeltaPrepareArgs;
+int rdl_delta_prepare(const DeltaPrepareArgs* a, void* stream);
 
 // ---- linear attention with a fixed decay per head (csrc/decay_attention.cu) ----
 // Per sequence and head, S_t = decay_h S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, with S [dim][vdim] in float, kept per
@@ -271,11 +329,16 @@ int rdl_latent_decode(void* out, long long out_stride, const void* q, long long 
 // ---- routed feed-forward (csrc/moe.cu) ----
 // sel[t, k], sel_w[t, k]: the `top` experts of row t by softmax score + correction, and their softmax scores;
 // logits: float work space [rows][experts] (two kernels: the logits, then softmax and choice)
+// scoring: RDL_ROUTE_SOFTMAX, or RDL_ROUTE_SIGMOID (every expert's score is sigmoid(logit) by itself)
+#define RDL_ROUTE_SOFTMAX 0
+#define RDL_ROUTE_SIGMOID 1
 int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                  int width, int top, int* sel, float* sel_w, float* logits, void* stream);
+                  int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream);
 // mid[(t, k), :] = gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real; w_gate_up [n_real][2 ff][width]
-int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, int n_rows, int top, int n_real,
-                    int ff, int width, int activation, float act_param, void* stream);
+// activation >= 16 (RDL_UNARY_*): experts of two matrices, mid = act(W_up[e] x_t) with w_gate_up [n_real][ff][width].
+// sel_w (optional): the pair's weight multiplies the expert's input, mid = f(W (sel_w[t, k] x_t)).
+int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, const float* sel_w, int n_rows,
+                    int top, int n_real, int ff, int width, int activation, float act_param, void* stream);
 // out[t, :] = sum_k sel_w[t, k] (e_k < n_real ? W_down[e_k] mid[(t, k), :] : x[t, :]); w_down [n_real][width][ff]
 int rdl_moe_down_combine(void* out, int dtype, const void* mid, const void* x, const void* w_down, const int* sel,
                          const float* sel_w, int n_rows, int top, int n_real, int ff, int width, void* stream);
@@ -285,7 +348,9 @@ int rdl_moe_down_combine(void* out, int dtype, const void* mid, const void* x, c
 // slot_pair[slot] (-1: padding), tile_group[tile] (-1: not in use).  Then the rows are gathered (bfloat16, width a
 // multiple of 8), multiplied tile by tile (rdl_gemm_tc_grouped) and summed per row with the router's weights.
 int rdl_moe_align(const int* sel, int n_pairs, int n_real, int max_tiles, int* pair_slot, int* slot_pair, int* tile_group, void* stream);
-int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, int max_tiles, int top, int width, void* stream);
+// rdl_moe_gather with sel_w: the gathered row is the pair's weight times x[t] (weights on the experts' inputs)
+int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, const float* sel_w, int max_tiles, int top,
+                   int width, void* stream);
 int rdl_moe_combine(void* out, const void* y, const void* x, const int* pair_slot, const float* sel_w, int n_rows, int top, int width,
                     void* stream);
 int rdl_gemm_tc_grouped(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k, int n_groups,

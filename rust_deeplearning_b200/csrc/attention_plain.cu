@@ -10,6 +10,7 @@
 //   keys kept: j <= p and (window == 0 or p - j < window)  ops.rs:905-922, :932-952
 //   a = softmax_j(s)                                      ops.rs:598-608
 //   (with sinks: the denominator also holds exp(sinks[h]); the reference has none)
+//   (with sigmoid_bias: a_j = sigmoid(s_j + sigmoid_bias[h]) for the keys kept, not normalised; the reference has none)
 //   o_h = sum_j a_j v_g,j                                 attention.rs:442-446
 // (paths within rustml/; attention.rs = nn/main/src/core/attention.rs).  The window holds for
 // single-token steps too, which the reference's cached path skips (attention.rs:429).
@@ -42,6 +43,8 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
+    const bool sig = a.sigmoid_bias != nullptr;
+    const float sig_bias = sig ? a.sigmoid_bias[h] : 0.f;
 
     for (int jb = (lo / 32) * 32; jb <= p; jb += 32) {
         const int j = jb + lane;
@@ -67,13 +70,18 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
             if (a.softcap > 0.f) d = a.softcap * tanhf(d / a.softcap);
             s = d;
         }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first block
-        const float pj = valid ? expf(s - m_new) : 0.f;
-        l = l * corr + warp_sum(pj);
-        m = m_new;
+        float pj;
+        if (sig) {
+            pj = valid ? 1.0f / (1.0f + expf(-(s + sig_bias))) : 0.f;
+        } else {
+            const float m_new = fmaxf(m, warp_max(s));
+            const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first block
+            pj = valid ? expf(s - m_new) : 0.f;
+            l = l * corr + warp_sum(pj);
+            m = m_new;
 #pragma unroll
-        for (int c = 0; c < CHUNKS; ++c) acc[c] *= corr;
+            for (int c = 0; c < CHUNKS; ++c) acc[c] *= corr;
+        }
         const unsigned long long vaddr = (unsigned long long)vp;
         for (int jj = 0; jj < 32; ++jj) {
             const int jk = jb + jj;
@@ -100,7 +108,7 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) acc[c] *= corr;
     }
-    const float inv = 1.0f / l;
+    const float inv = sig ? 1.0f : 1.0f / l;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int d = c * 32 + lane;
@@ -125,6 +133,7 @@ int rdl_check_attention_args(const AttentionArgs* a, const char* who) {
                     a->page_size, a->ring_pages, a->table_width);
     }
     RDL_REQUIRE(a->tables || (a->k_new && a->v_new), "%s: neither a cache nor new keys and values", who);
+    RDL_REQUIRE(!(a->sigmoid_bias && a->sinks), "%s: sigmoid weights have no denominator for sinks to join", who);
     return 0;
 }
 

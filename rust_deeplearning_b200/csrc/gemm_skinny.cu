@@ -407,6 +407,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
                 }
                 float y = v0;
                 if (GATED) y = rdl_activation(v0, a.activation) * v1;
+                else if (a.activation >= 16) y = rdl_unary(v0, a.activation);     // an element-wise activation of the plain form
                 if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
                 rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
             }

@@ -164,6 +164,11 @@ __device__ __forceinline__ void epilogue_piece(const TcArgs& a, uint32_t taddr, 
             for (int i = 0; i < 32; ++i) v[i] = rdl_activation_fast(v[i], act) * u[i];
         }
     }
+    if (!GATED && a.activation >= 16) {                    // an element-wise activation of the plain form (RDL_UNARY_*)
+        const int act = a.activation;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = rdl_unary_fast(v[i], act);
+    }
     if (a.softcap > 0.f) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);

@@ -1,11 +1,13 @@
 // Routed feed-forward (mixture of experts): the router, and the experts for few rows.
 //
 // Router, per row x (float arithmetic throughout):
-//   z = W_r x,  s = softmax(z) over all experts (identity experts included),
+//   z = W_r x,  s = softmax(z) over all experts (identity experts included), or s = sigmoid(z) expert by expert,
 //   choice = s + correction;  the `top` largest choices are taken (ties: the lower index),
 //   their weights are s itself (not renormalised).
 // An expert e < n_real is a gated feed-forward, y = W_down act(W_gate x, W_up x); an expert e >= n_real is
 // an identity expert whose output is x.  The row's result is sum_k weight_k y_k in the order of the choice.
+// Two further forms: experts of two matrices, y = W_down act(W_up x) (activation codes RDL_UNARY_*), and weights
+// that multiply an expert's input instead of its output, y_k = expert(weight_k x), summed with weight one.
 //
 // Few rows (single-token steps, the 32-bit path): every (row, choice) pair streams its expert's
 // matrices, a warp per output value (rdl_moe_gate_up, rdl_moe_down_combine); the sums run lane by lane
@@ -132,7 +134,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* _
 constexpr int TOPK_WARPS = 4;
 
 __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n_rows,
-                                                                   int n_experts, int top, int* __restrict__ sel, float* __restrict__ sel_w) {
+                                                                   int n_experts, int top, int scoring, int* __restrict__ sel,
+                                                                   float* __restrict__ sel_w) {
     extern __shared__ float zs_all[];          // per warp: [n_experts] scores, [n_experts] choices
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -143,18 +146,23 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
     float* choice = zs + n_experts;
     const float* zr = z + (long long)t * n_experts;
     float m = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, zr[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) {
-        const float p = expf(zr[e] - m);
-        zs[e] = p;
-        sum += p;
+    float sum = 1.f;
+    if (scoring == RDL_ROUTE_SIGMOID) {
+        for (int e = lane; e < n_experts; e += 32) zs[e] = 1.0f / (1.0f + expf(-zr[e]));
+    } else {
+        for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, zr[e]);
+        m = warp_max(m);
+        sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = expf(zr[e] - m);
+            zs[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
     }
-    sum = warp_sum(sum);
     __syncwarp();
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = zs[e] / sum;
+        const float s = scoring == RDL_ROUTE_SIGMOID ? zs[e] : zs[e] / sum;
         zs[e] = s;
         choice[e] = s + (correction ? correction[e] : 0.f);
     }
@@ -249,10 +257,12 @@ __device__ __forceinline__ float lane_dot(const T* a, const T* b, int n, int lan
 
 // mid[p, j] = act(W_gate[e] x, W_up[e] x)[j] for pair p = (row t, choice k) with expert e = sel[p] < n_real.
 // w: [n_real][2 ff][width], an expert's gate rows followed by its up rows.  A warp per (pair, j).
+// activation >= 16: experts of two matrices, w [n_real][ff][width], mid = act(W_up[e] x).  sel_w given: the pair's weight
+// multiplies the expert's input; a product is linear in it, so it multiplies the float sums instead of every term.
 template <typename T>
 __global__ void __launch_bounds__(PAIR_WARPS * 32) moe_gate_up_kernel(T* __restrict__ mid, const T* __restrict__ x, const T* __restrict__ w,
-                                                                      const int* __restrict__ sel, int top, int n_real, int ff, int width,
-                                                                      int activation, float act_param) {
+                                                                      const int* __restrict__ sel, const float* __restrict__ sel_w, int top,
+                                                                      int n_real, int ff, int width, int activation, float act_param) {
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const int p = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -261,12 +271,19 @@ __global__ void __launch_bounds__(PAIR_WARPS * 32) moe_gate_up_kernel(T* __restr
     const int j = blockIdx.x * PAIR_WARPS + warp;
     if (j >= ff) return;
     const T* row = x + (long long)(p / top) * width;
+    const float in_w = sel_w ? sel_w[p] : 1.0f;
+    if (activation >= 16) {
+        const float u = warp_sum(lane_dot<T>(w + ((long long)e * ff + j) * width, row, width, lane)) * in_w;
+        const float r = fmaxf(u, 0.f);
+        if (lane == 0) mid[(long long)p * ff + j] = from_float<T>(activation == RDL_UNARY_RELU2 ? r * r : u / (1.0f + expf(-u)));
+        return;
+    }
     const T* wg = w + ((long long)e * 2 * ff + j) * width;
     const T* wu = wg + (long long)ff * width;
     float g, u;
     lane_dot2<T>(wg, wu, row, width, lane, g, u);
-    g = warp_sum(g);
-    u = warp_sum(u);
+    g = warp_sum(g) * in_w;
+    u = warp_sum(u) * in_w;
     if (lane == 0) mid[(long long)p * ff + j] = from_float<T>(rdl_gated(g, u, activation, act_param));
 }
 
@@ -285,7 +302,7 @@ __global__ void __launch_bounds__(PAIR_WARPS * 32) moe_down_combine_kernel(T* __
     for (int k = 0; k < top; ++k) {
         const int p = t * top + k;
         const int e = sel[p];
-        const float wk = sel_w[p];
+        const float wk = sel_w ? sel_w[p] : 1.0f;
         float y;
         if (e >= n_real) {
             y = to_float(x[(long long)t * width + n]);
@@ -359,7 +376,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS) moe_align_kernel(const int* __r
 
 // xs[slot, :] = x[pair / top, :] (zeros in padding slots of tiles in use); 16-byte pieces
 __global__ void moe_gather_kernel(uint4* __restrict__ xs, const uint4* __restrict__ x, const int* __restrict__ slot_pair,
-                                  const int* __restrict__ tile_group, int top, int pieces) {
+                                  const int* __restrict__ tile_group, const float* __restrict__ sel_w, int top, int pieces) {
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const int slot = blockIdx.x;
@@ -370,7 +387,21 @@ __global__ void moe_gather_kernel(uint4* __restrict__ xs, const uint4* __restric
         for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
     } else {
         const uint4* src = x + (long long)(p / top) * pieces;
-        for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
+        if (!sel_w) {
+            for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
+        } else {
+            const float wk = sel_w[p];
+            for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+                uint4 raw = src[i];
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 v = __bfloat1622float2(h[k]);
+                    h[k] = __floats2bfloat162_rn(v.x * wk, v.y * wk);
+                }
+                dst[i] = raw;
+            }
+        }
     }
 }
 
@@ -386,7 +417,7 @@ __global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_b
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
         for (int k = 0; k < top; ++k) {
             const int slot = pair_slot[t * top + k];
-            const float wk = sel_w[t * top + k];
+            const float wk = sel_w ? sel_w[t * top + k] : 1.0f;
             const __nv_bfloat16* src = slot >= 0 ? y + (long long)slot * width + c : x + (long long)t * width + c;
             const uint4 raw = *reinterpret_cast<const uint4*>(src);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -408,10 +439,11 @@ __global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_b
 }  // namespace
 
 extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                             int width, int top, int* sel, float* sel_w, float* logits, void* stream) {
+                             int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "moe_route: bad dtype %d", dtype);
     RDL_REQUIRE(x && w_router && sel && sel_w && logits && n_experts > 0 && width > 0, "moe_route: bad arguments");
     RDL_REQUIRE(top >= 1 && top <= n_experts, "moe_route: %d of %d experts cannot be chosen", top, n_experts);
+    RDL_REQUIRE(scoring == RDL_ROUTE_SOFTMAX || scoring == RDL_ROUTE_SIGMOID, "moe_route: unknown scoring %d", scoring);
     RDL_REQUIRE(n_experts <= 1024, "moe_route: %d experts exceed the 1,024 the router kernels hold", n_experts);
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -431,32 +463,33 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
     }
     const size_t smem = (size_t)TOPK_WARPS * 2 * n_experts * sizeof(float);
     RDL_CHECK_EX(rdl_launch(moe_topk_kernel, dim3((n_rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(TOPK_WARPS * 32), smem, st, (const float*)logits,
-                            correction, n_rows, n_experts, top, sel, sel_w), "moe_route");
+                            correction, n_rows, n_experts, top, scoring, sel, sel_w), "moe_route");
     return 0;
 }
 
-extern "C" int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, int n_rows, int top, int n_real,
-                               int ff, int width, int activation, float act_param, void* stream) {
+extern "C" int rdl_moe_gate_up(void* mid, int dtype, const void* x, const void* w_gate_up, const int* sel, const float* sel_w, int n_rows,
+                               int top, int n_real, int ff, int width, int activation, float act_param, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "moe_gate_up: bad dtype %d", dtype);
     RDL_REQUIRE(mid && x && sel && (w_gate_up || n_real == 0) && top > 0 && ff > 0 && width > 0, "moe_gate_up: bad arguments");
-    RDL_REQUIRE(rdl_gated_known(activation), "moe_gate_up: unknown activation %d", activation);
+    RDL_REQUIRE(rdl_gated_known(activation) || activation == RDL_UNARY_RELU2 || activation == RDL_UNARY_SILU,
+                "moe_gate_up: unknown activation %d", activation);
     if (n_rows == 0 || n_real == 0) return 0;
     RDL_REQUIRE((long long)n_rows * top <= 65535, "moe_gate_up: %d rows x %d choices exceed the grid limit", n_rows, top);
     const dim3 grid((ff + PAIR_WARPS - 1) / PAIR_WARPS, n_rows * top);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == RDL_BF16)
         RDL_CHECK_EX(rdl_launch(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(PAIR_WARPS * 32), 0, st, (__nv_bfloat16*)mid, (const __nv_bfloat16*)x,
-                                (const __nv_bfloat16*)w_gate_up, sel, top, n_real, ff, width, activation, act_param), "moe_gate_up");
+                                (const __nv_bfloat16*)w_gate_up, sel, sel_w, top, n_real, ff, width, activation, act_param), "moe_gate_up");
     else
         RDL_CHECK_EX(rdl_launch(moe_gate_up_kernel<float>, grid, dim3(PAIR_WARPS * 32), 0, st, (float*)mid, (const float*)x, (const float*)w_gate_up,
-                                sel, top, n_real, ff, width, activation, act_param), "moe_gate_up");
+                                sel, sel_w, top, n_real, ff, width, activation, act_param), "moe_gate_up");
     return 0;
 }
 
 extern "C" int rdl_moe_down_combine(void* out, int dtype, const void* mid, const void* x, const void* w_down, const int* sel,
                                     const float* sel_w, int n_rows, int top, int n_real, int ff, int width, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "moe_down_combine: bad dtype %d", dtype);
-    RDL_REQUIRE(out && x && sel && sel_w && ((mid && w_down) || n_real == 0) && top > 0 && width > 0, "moe_down_combine: bad arguments");
+    RDL_REQUIRE(out && x && sel && ((mid && w_down) || n_real == 0) && top > 0 && width > 0, "moe_down_combine: bad arguments");
     if (n_rows == 0) return 0;
     RDL_REQUIRE(n_rows <= 65535, "moe_down_combine: %d rows exceed the grid limit", n_rows);
     const dim3 grid((width + PAIR_WARPS - 1) / PAIR_WARPS, n_rows);
@@ -483,19 +516,19 @@ extern "C" int rdl_moe_align(const int* sel, int n_pairs, int n_real, int max_ti
     return 0;
 }
 
-extern "C" int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, int max_tiles, int top, int width,
-                              void* stream) {
+extern "C" int rdl_moe_gather(void* xs, const void* x, const int* slot_pair, const int* tile_group, const float* sel_w, int max_tiles,
+                              int top, int width, void* stream) {
     RDL_REQUIRE(xs && x && slot_pair && tile_group && max_tiles > 0 && top > 0 && width > 0 && width % 8 == 0,
                 "moe_gather: bad arguments (bfloat16 rows of a multiple of 8 values)");
     RDL_REQUIRE((uintptr_t)xs % 16 == 0 && (uintptr_t)x % 16 == 0, "moe_gather: rows must start on 16-byte boundaries");
     RDL_CHECK_EX(rdl_launch(moe_gather_kernel, dim3(max_tiles * MOE_TILE), dim3(128), 0, (cudaStream_t)stream, (uint4*)xs, (const uint4*)x, slot_pair,
-                            tile_group, top, width / 8), "moe_gather");
+                            tile_group, sel_w, top, width / 8), "moe_gather");
     return 0;
 }
 
 extern "C" int rdl_moe_combine(void* out, const void* y, const void* x, const int* pair_slot, const float* sel_w, int n_rows, int top,
                                int width, void* stream) {
-    RDL_REQUIRE(out && y && x && pair_slot && sel_w && n_rows > 0 && top > 0 && width > 0 && width % 8 == 0,
+    RDL_REQUIRE(out && y && x && pair_slot && n_rows > 0 && top > 0 && width > 0 && width % 8 == 0,
                 "moe_combine: bad arguments (bfloat16 rows of a multiple of 8 values)");
     RDL_REQUIRE((uintptr_t)out % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)x % 16 == 0, "moe_combine: rows must start on 16-byte boundaries");
     RDL_CHECK_EX(rdl_launch(moe_combine_kernel, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)y,

@@ -144,7 +144,8 @@ __global__ void __launch_bounds__(256) norm_pair_vec_kernel(float* __restrict__ 
 template <typename TO, bool WARP, int NIT>
 __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, long long n_items, int groups,
                                                                   int group, const void* __restrict__ w, int w_dtype, float eps,
-                                                                  const void* __restrict__ g, long long g_stride, int g_dtype, int act) {
+                                                                  const void* __restrict__ g, long long g_stride, int g_dtype, int act,
+                                                                  int gate_first) {
     __shared__ float scratch[33];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -161,6 +162,10 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
         if (e < group) {
             rn_load4(x + base + e, v[it]);
             if (g) rn_load4(g, t * g_stride + col0 + e, g_dtype, gv[it]);
+            if (g && gate_first) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[it][k] *= gate_value(gv[it][k], act);
+            }
         }
     }
     float ss = 0.f;
@@ -184,7 +189,7 @@ __global__ void __launch_bounds__(256) group_norm_gate_vec_kernel(TO* __restrict
             for (int k = 0; k < 4; ++k) {
                 o[k] = v[it][k] * inv;
                 if (w) o[k] *= wv[k];
-                if (g) o[k] *= sizeof(TO) == 2 ? gate_value_fast(gv[it][k], act) : gate_value(gv[it][k], act);
+                if (g && !gate_first) o[k] *= sizeof(TO) == 2 ? gate_value_fast(gv[it][k], act) : gate_value(gv[it][k], act);
             }
             rn_store4(out + base + e, o);
         }
@@ -399,7 +404,8 @@ extern "C" int rdl_gate_mul(void* out, long long out_stride, const void* x, long
 // float rows normed group by group, times an optional weight and an optional gate
 template <typename TO>
 __global__ void group_norm_gate_kernel(TO* __restrict__ out, const float* __restrict__ x, int groups, int group, const void* __restrict__ w,
-                                       int w_dtype, float eps, const void* __restrict__ g, long long g_stride, int g_dtype, int act) {
+                                       int w_dtype, float eps, const void* __restrict__ g, long long g_stride, int g_dtype, int act,
+                                       int gate_first) {
     __shared__ float scratch[33];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -407,22 +413,27 @@ __global__ void group_norm_gate_kernel(TO* __restrict__ out, const float* __rest
     const long long base = ((long long)t * groups + gi) * group;
     const int col0 = gi * group;
     float ss = 0.f;
+    const bool first = g && gate_first;
     for (int i = threadIdx.x; i < group; i += blockDim.x) {
-        const float v = x[base + i];
+        float v = x[base + i];
+        if (first) v *= gate_value(rdl_load(g, (long long)t * g_stride + col0 + i, g_dtype), act);
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)group + eps);
     for (int i = threadIdx.x; i < group; i += blockDim.x) {
-        float v = x[base + i] * inv;
+        float v = x[base + i];
+        if (first) v *= gate_value(rdl_load(g, (long long)t * g_stride + col0 + i, g_dtype), act);
+        v *= inv;
         if (w) v *= rdl_load(w, col0 + i, w_dtype);
-        if (g) v *= gate_value(rdl_load(g, (long long)t * g_stride + col0 + i, g_dtype), act);
+        if (g && !first) v *= gate_value(rdl_load(g, (long long)t * g_stride + col0 + i, g_dtype), act);
         out[base + i] = from_float<TO>(v);
     }
 }
 
 extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int n_rows, int groups, int group, const void* w,
-                                   int w_dtype, float eps, const void* g, long long g_stride, int g_dtype, int gate_act, void* stream) {
+                                   int w_dtype, float eps, const void* g, long long g_stride, int g_dtype, int gate_act, int gate_first,
+                                   void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(out_dtype) && rdl_valid_dtype(w_dtype) && rdl_valid_dtype(g_dtype), "group_norm_gate: bad dtype");
     RDL_REQUIRE(out && x && n_rows >= 0 && groups > 0 && groups <= 65535 && group > 0, "group_norm_gate: bad sizes");
     RDL_REQUIRE(gate_act == RDL_GATE_SIGMOID || gate_act == RDL_GATE_SILU, "group_norm_gate: unknown gate %d", gate_act);
@@ -441,14 +452,14 @@ extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int
     do {                                                                                                                                 \
         if (out_dtype == RDL_BF16) {                                                                                                     \
             if (warp) e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, true, N>, grid, block, 0, st, (__nv_bfloat16*)out, x,     \
-                                     n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                           \
+                                     n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act, gate_first);               \
             else e = rdl_launch(group_norm_gate_vec_kernel<__nv_bfloat16, false, N>, grid, block, 0, st, (__nv_bfloat16*)out, x,         \
-                                n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                \
+                                n_items, groups, group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act, gate_first);                    \
         } else {                                                                                                                         \
             if (warp) e = rdl_launch(group_norm_gate_vec_kernel<float, true, N>, grid, block, 0, st, (float*)out, x, n_items, groups,    \
-                                     group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                            \
+                                     group, w, w_dtype, eps, g, g_stride, g_dtype, gate_act, gate_first);                                \
             else e = rdl_launch(group_norm_gate_vec_kernel<float, false, N>, grid, block, 0, st, (float*)out, x, n_items, groups, group, \
-                                w, w_dtype, eps, g, g_stride, g_dtype, gate_act);                                                        \
+                                w, w_dtype, eps, g, g_stride, g_dtype, gate_act, gate_first);                                            \
         }                                                                                                                                \
     } while (0)
             RN_BY_DEPTH(vec_depth(group, warp ? 32 : vt), GROUP_NORM_LAUNCH)
@@ -460,10 +471,10 @@ extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int
     const dim3 grid(n_rows, groups), block(group <= 64 ? 32 : row_threads(group));
     if (out_dtype == RDL_BF16)
         e = rdl_launch(group_norm_gate_kernel<__nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, x, groups, group, w, w_dtype, eps, g,
-                       g_stride, g_dtype, gate_act);
+                       g_stride, g_dtype, gate_act, gate_first);
     else
         e = rdl_launch(group_norm_gate_kernel<float>, grid, block, 0, st, (float*)out, x, groups, group, w, w_dtype, eps, g, g_stride,
-                       g_dtype, gate_act);
+                       g_dtype, gate_act, gate_first);
     RDL_CHECK_EX(e, "group_norm_gate");
     return 0;
 }

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -172,7 +172,7 @@ class AttentionArgs(ctypes.Structure):
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
         ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
         ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p), ("rotary_dim", ctypes.c_int), ("new_rows", ctypes.c_int),
-        ("sinks", ctypes.c_void_p),
+        ("sinks", ctypes.c_void_p), ("sigmoid_bias", ctypes.c_void_p),
         ("wait_cycles", ctypes.c_longlong), ("test_extra_tx", ctypes.c_int),     # filled in by the launcher
     ]
 
@@ -251,6 +251,39 @@ class DecayAttentionArgs(ctypes.Structure):
     ]
 
 
+class RecurrenceArgs(ctypes.Structure):
+    """One call of a recurrence whose decay depends on the token (`csrc/api.h`)."""
+    _fields_ = [
+        ("dtype", ctypes.c_int), ("mode", ctypes.c_int),
+        ("n_tokens", ctypes.c_int), ("n_seqs", ctypes.c_int), ("n_heads", ctypes.c_int), ("n_key_heads", ctypes.c_int),
+        ("dim", ctypes.c_int), ("vdim", ctypes.c_int),
+        ("rows", ctypes.c_void_p), ("row_stride", ctypes.c_longlong),
+        ("q_col", ctypes.c_int), ("k_col", ctypes.c_int), ("v_col", ctypes.c_int),
+        ("dt_rows", ctypes.c_void_p), ("dt_stride", ctypes.c_longlong),
+        ("dt_bias", ctypes.c_void_p), ("a_log", ctypes.c_void_p), ("d_skip", ctypes.c_void_p),
+        ("q_f", ctypes.c_void_p), ("k_f", ctypes.c_void_p), ("g_f", ctypes.c_void_p), ("beta_f", ctypes.c_void_p),
+        ("tok_pos", ctypes.c_void_p), ("seq_start", ctypes.c_void_p), ("slots", ctypes.c_void_p),
+        ("state", ctypes.c_void_p), ("out", ctypes.c_void_p),
+    ]
+
+
+REC_SSM, REC_DELTA = 0, 1
+
+
+class DeltaPrepareArgs(ctypes.Structure):
+    """What enters a delta-rule recurrence, made in float from the projections' rows (`csrc/api.h`)."""
+    _fields_ = [
+        ("dtype", ctypes.c_int), ("bias_dtype", ctypes.c_int),
+        ("n_tokens", ctypes.c_int), ("n_heads", ctypes.c_int), ("n_key_heads", ctypes.c_int), ("dim", ctypes.c_int),
+        ("rows", ctypes.c_void_p), ("row_stride", ctypes.c_longlong), ("q_col", ctypes.c_int), ("k_col", ctypes.c_int),
+        ("decay_rows", ctypes.c_void_p), ("decay_stride", ctypes.c_longlong),
+        ("beta_rows", ctypes.c_void_p), ("beta_stride", ctypes.c_longlong),
+        ("dt_bias", ctypes.c_void_p), ("a_log", ctypes.c_void_p),
+        ("q_scale", ctypes.c_float), ("unit_eps", ctypes.c_float),
+        ("q_f", ctypes.c_void_p), ("k_f", ctypes.c_void_p), ("g_f", ctypes.c_void_p), ("beta_f", ctypes.c_void_p),
+    ]
+
+
 class SamplingArgs(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_k", ctypes.c_int), ("top_p", ctypes.c_float),
                 ("repetition_penalty", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
@@ -274,7 +307,13 @@ _SIGNATURES = {
     "rdl_postnorm": [_P, _P, _I, _F, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "rdl_norm_pair": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _I, _I, _P],
     "rdl_gate_mul": [_P, _LL, _P, _LL, _P, _LL, _I, _I, _I, _I, _P],
-    "rdl_group_norm_gate": [_P, _I, _P, _I, _I, _I, _P, _I, _F, _P, _LL, _I, _I, _P],
+    "rdl_group_norm_gate": [_P, _I, _P, _I, _I, _I, _P, _I, _F, _P, _LL, _I, _I, _I, _P],
+    "rdl_norm_shift": [_P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "rdl_short_conv": [_P, _LL, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "rdl_gated_residual_add": [_P, _P, _LL, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "rdl_activation_inplace": [_P, _I, _LL, _I, _P],
+    "rdl_recurrence_scan": [ctypes.POINTER(RecurrenceArgs), _P],
+    "rdl_delta_prepare": [ctypes.POINTER(DeltaPrepareArgs), _P],
     "rdl_decay_attention_scan": [ctypes.POINTER(DecayAttentionArgs), _P],
     "rdl_decay_attention_chunked": [ctypes.POINTER(DecayAttentionArgs), _P, _LL, _P],
     "rdl_decay_attention_chunks": [_I, _I],
@@ -292,11 +331,11 @@ _SIGNATURES = {
     "rdl_gate_heads": [_P, _I, _P, _LL, _I, _P, _LL, _I, _I, _I, _P],
     "rdl_heads_linear": [ctypes.POINTER(HeadsLinearArgs), _P],
     "rdl_latent_decode": [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _LL, _P],
-    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P],
-    "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "rdl_moe_down_combine": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "rdl_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P],
-    "rdl_moe_gather": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "rdl_moe_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "rdl_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_tc_grouped": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P],
 }

@@ -228,9 +228,10 @@ def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: str) -> torch.Tensor:
 
 def group_norm_gate(x: torch.Tensor, groups: int, *, eps: float, weight: Optional[torch.Tensor] = None,
                     gate: Optional[torch.Tensor] = None, gate_kind: str = "sigmoid",
-                    out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                    out_dtype: torch.dtype = torch.float32, gate_first: bool = False) -> torch.Tensor:
     """float32 rows [rows, groups * n] normed group by group (v / sqrt(mean(v^2) + eps)), times weight[column] if
-    given, times gate_fn(gate[row, column]) if given (gate may be a column slice of wider rows); result in out_dtype."""
+    given, times gate_fn(gate[row, column]) if given (gate may be a column slice of wider rows); result in out_dtype.
+    gate_first: the gate multiplies the values before the norm, so that the root mean square is that of the gated values."""
     _need(x.dtype is torch.float32 and x.dim() == 2 and x.is_contiguous() and x.shape[1] % groups == 0,
           "group_norm_gate: contiguous float32 rows whose width the groups divide")
     _need(gate_kind in GATES, f"unknown gate '{gate_kind}', known: {sorted(GATES)}")
@@ -243,7 +244,7 @@ def group_norm_gate(x: torch.Tensor, groups: int, *, eps: float, weight: Optiona
     library.check(library.load().rdl_group_norm_gate(
         _ptr(out), _dtype_code(out), _ptr(x), rows, groups, width // groups, _ptr(weight),
         _dtype_code(weight) if weight is not None else 0, float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0,
-        _dtype_code(gate) if gate is not None else 0, GATES[gate_kind], _stream(x)))
+        _dtype_code(gate) if gate is not None else 0, GATES[gate_kind], int(bool(gate_first)), _stream(x)))
     return out
 
 
@@ -444,19 +445,30 @@ def _linear_deferred(x: DeferredRows, weight: torch.Tensor, n_out: int, out_dtyp
     return out
 
 
+def activation_(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """An element-wise activation of `UNARY_FORMS` on a dense tensor, in place (float arithmetic)."""
+    _need(kind in UNARY_FORMS, f"unknown activation '{kind}', known: {sorted(UNARY_FORMS)}")
+    _need(x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16), "activation_: a dense float32 or bfloat16 tensor")
+    library.check(library.load().rdl_activation_inplace(_ptr(x), _dtype_code(x), x.numel(), UNARY_FORMS[kind], _stream(x)))
+    return x
+
+
 def linear(x, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           softcap: Optional[float] = None, status: Optional[torch.Tensor] = None):
+           softcap: Optional[float] = None, status: Optional[torch.Tensor] = None, activation: Optional[str] = None):
     """x [rows, in] times weight [out, in] transposed; optionally cap * tanh(. / cap) on the result.
-    x may be `DeferredRows` (the rows after a deferred norm).
+    x may be `DeferredRows` (the rows after a deferred norm).  activation: an element-wise form of `UNARY_FORMS`
+    on the result (the product's epilogue in the library's own bfloat16 kernels, a kernel of its own elsewhere).
 
     float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
     bfloat16: up to 16 rows (decode) the weight-streaming tensor-core kernels, from 128 rows the TMA +
     tcgen05 kernels, all with float accumulation and the soft-cap in their epilogue.  17 to 127 rows, and
     operands that do not meet the alignment rules, go to a library product (cuBLAS through torch), which
     is what the reference's engine uses for all its products."""
+    _need(activation is None or (activation in UNARY_FORMS and softcap is None),
+          f"linear: activation '{activation}' is not one of {sorted(UNARY_FORMS)} (and comes without a soft-cap)")
     if isinstance(x, DeferredRows):
         _need(softcap is None or out_dtype is torch.float32, "linear: the soft-cap is applied to float32 results")
-        out = _linear_deferred(x, weight, weight.shape[0], out_dtype or x.dtype, False, 0, softcap, status)
+        out = _linear_deferred(x, weight, weight.shape[0], out_dtype or x.dtype, False, 0, softcap, status) if activation is None else None
         if out is not None:
             return out
         x = x.materialise()
@@ -472,12 +484,14 @@ def linear(x, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         library.check(library.load().rdl_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0],
                                                   x.shape[1], _stream(x)))
     elif _own_bf16_kernel(x, weight):
-        return _gemm_bf16(x, weight, weight.shape[0], out_dtype, False, 0, softcap, status)
+        return _gemm_bf16(x, weight, weight.shape[0], out_dtype, False, UNARY_FORMS[activation] if activation else 0, softcap, status)
     else:
         _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
         out = torch.mm(x, weight.t(), out_dtype=torch.float32) if out_dtype is torch.float32 else torch.mm(x, weight.t())
     if softcap is not None:
         softcap_(out, softcap)
+    if activation is not None:
+        activation_(out, activation)
     return out
 
 
@@ -635,7 +649,7 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
               scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None,
               rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None,
-              sinks: Optional[torch.Tensor] = None):
+              sinks: Optional[torch.Tensor] = None, sigmoid_bias: Optional[torch.Tensor] = None):
     """Attention of the step's tokens over cache and new rows.
 
     q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
@@ -655,6 +669,8 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     them.  The packed rows themselves stay as they are.
     sinks: float32 [n_heads] - a logit per head without key or value whose exponential joins the softmax's
     denominator once (neither scaled nor capped).
+    sigmoid_bias: float32 [n_heads] - no softmax: the weight of a visible key is sigmoid(score + sigmoid_bias[h]) and the
+    weights are not normalised over the keys.
     Returns [tokens, n_heads * head_dim] in the dtype of q."""
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim, "attention: bad query rows")
     T = q.shape[0]
@@ -676,6 +692,11 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         _need(sinks.dtype is torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads and sinks.device == q.device,
               "attention: sinks must be float32 [n_heads]")
         a.sinks = sinks.data_ptr()
+    if sigmoid_bias is not None:
+        _need(sigmoid_bias.dtype is torch.float32 and sigmoid_bias.is_contiguous() and sigmoid_bias.numel() == n_heads
+              and sigmoid_bias.device == q.device, "attention: sigmoid_bias must be float32 [n_heads]")
+        _need(sinks is None, "attention: sigmoid weights have no denominator for sinks to join")
+        a.sigmoid_bias = sigmoid_bias.data_ptr()
     fast_ok = q.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if kind == "auto":
         kind = "prefill" if fast_ok and b.n_tiles > 0 else "plain"
@@ -961,11 +982,20 @@ def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads
 
 # gated forms with a parameter (`csrc/activations.cuh`): name -> code
 GATED_FORMS = dict(ACTIVATIONS, swish_limit=2)
+# element-wise activations of a product that is not gated (`csrc/api.h`, RDL_UNARY_*): experts of two matrices,
+# y = W_down act(W_up x), take these as their `form`
+UNARY_FORMS = {"relu2": 16, "silu_plain": 17}
+EXPERT_FORMS = dict(GATED_FORMS, **UNARY_FORMS)
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int):
-    """Per row: softmax over all experts of the float32 logits W_r x; the `top` experts with the largest score +
-    correction (int32 [rows, top]) and their scores without it (float32 [rows, top])."""
+ROUTE_SCORING = {"softmax": 0, "sigmoid": 1}     # `csrc/api.h`, RDL_ROUTE_*
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scoring: str = "softmax"):
+    """Per row: scores of all experts from the float32 logits W_r x (softmax over the experts, or sigmoid expert by
+    expert); the `top` experts with the largest score + correction (int32 [rows, top]) and their scores without it
+    (float32 [rows, top])."""
+    _need(scoring in ROUTE_SCORING, f"moe_route: unknown scoring '{scoring}', known: {sorted(ROUTE_SCORING)}")
     _dense(x, "x")
     _need(w_router.dtype is torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1], "moe_route: float32 router [experts, width]")
     E = w_router.shape[0]
@@ -975,7 +1005,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     sel_w = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
     logits = torch.empty((x.shape[0], E), dtype=torch.float32, device=x.device)
     library.check(library.load().rdl_moe_route(_ptr(x), _dtype_code(x), _ptr(w_router), _ptr(correction), x.shape[0], E, x.shape[1], top,
-                                               _ptr(sel), _ptr(sel_w), _ptr(logits), _stream(x)), 2)
+                                               ROUTE_SCORING[scoring], _ptr(sel), _ptr(sel_w), _ptr(logits), _stream(x)), 2)
     return sel, sel_w
 
 
@@ -983,20 +1013,24 @@ MOE_PAIR_ROWS = 4096     # rows of one launch of the per-pair expert kernels (th
 
 
 def moe_experts_few(x: torch.Tensor, sel: torch.Tensor, sel_w: torch.Tensor, w_gate_up: Optional[torch.Tensor],
-                    w_down: Optional[torch.Tensor], n_real: int, form: str, param: float) -> torch.Tensor:
+                    w_down: Optional[torch.Tensor], n_real: int, form: str, param: float,
+                    weights_on_input: bool = False) -> torch.Tensor:
     """The routed experts with every (row, choice) pair streaming its expert's matrices: out[t] = sum_k sel_w[t, k] y_k,
     y_k = W_down[e] gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real, else x_t (an identity expert).
-    w_gate_up: [n_real, 2 ff, width] (an expert's gate rows, then its up rows); w_down: [n_real, width, ff]."""
+    w_gate_up: [n_real, 2 ff, width] (an expert's gate rows, then its up rows); w_down: [n_real, width, ff].
+    form in UNARY_FORMS: experts of two matrices, y_k = W_down[e] act(W_up[e] x_t), with w_gate_up [n_real, ff, width].
+    weights_on_input: y_k = expert(sel_w[t, k] x_t) and out[t] = sum_k y_k."""
     _dense(x, "x")
     T, width = x.shape
     top = sel.shape[1]
-    _need(form in GATED_FORMS, f"unknown gated form '{form}', known: {sorted(GATED_FORMS)}")
+    _need(form in EXPERT_FORMS, f"unknown expert form '{form}', known: {sorted(EXPERT_FORMS)}")
+    per = 1 if form in UNARY_FORMS else 2
     ff = 0
     if n_real:
         _need(w_gate_up.dtype is x.dtype and w_down.dtype is x.dtype and w_gate_up.is_contiguous() and w_down.is_contiguous()
-              and w_gate_up.dim() == 3 and w_gate_up.shape[0] == n_real and w_gate_up.shape[2] == width and w_gate_up.shape[1] % 2 == 0
-              and tuple(w_down.shape) == (n_real, width, w_gate_up.shape[1] // 2), "moe_experts_few: expert matrices do not fit")
-        ff = w_gate_up.shape[1] // 2
+              and w_gate_up.dim() == 3 and w_gate_up.shape[0] == n_real and w_gate_up.shape[2] == width and w_gate_up.shape[1] % per == 0
+              and tuple(w_down.shape) == (n_real, width, w_gate_up.shape[1] // per), "moe_experts_few: expert matrices do not fit")
+        ff = w_gate_up.shape[1] // per
     out = torch.empty_like(x)
     lib = library.load()
     step = max(1, min(MOE_PAIR_ROWS, 65535 // top))
@@ -1006,9 +1040,11 @@ def moe_experts_few(x: torch.Tensor, sel: torch.Tensor, sel_w: torch.Tensor, w_g
         mid = None
         if n_real:
             mid = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
-            library.check(lib.rdl_moe_gate_up(_ptr(mid), _dtype_code(x), _ptr(xs), _ptr(w_gate_up), _ptr(ss), n, top, n_real, ff, width,
-                                              GATED_FORMS[form], float(param), _stream(x)))
-        library.check(lib.rdl_moe_down_combine(_ptr(os_), _dtype_code(x), _ptr(mid), _ptr(xs), _ptr(w_down), _ptr(ss), _ptr(sw), n, top,
+            library.check(lib.rdl_moe_gate_up(_ptr(mid), _dtype_code(x), _ptr(xs), _ptr(w_gate_up), _ptr(ss),
+                                              _ptr(sw) if weights_on_input else None, n, top, n_real, ff, width,
+                                              EXPERT_FORMS[form], float(param), _stream(x)))
+        library.check(lib.rdl_moe_down_combine(_ptr(os_), _dtype_code(x), _ptr(mid), _ptr(xs), _ptr(w_down), _ptr(ss),
+                                               None if weights_on_input else _ptr(sw), n, top,
                                                n_real, max(ff, 1), width, _stream(x)))
     return out
 
@@ -1018,13 +1054,14 @@ MOE_GROUPED_MIN_PAIRS = 128  # from this many (row, choice) pairs on the rows ar
 
 
 def moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float,
-                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        status: Optional[torch.Tensor] = None, weights_on_input: bool = False) -> torch.Tensor:
     """The routed experts for many rows in bfloat16: pairs sorted by expert into tiles of 128 rows, both products on the
     tcgen05 kernel with one expert per row tile, then the weighted sum per row.  No step of it needs the host to
     know the counts: the buffers are sized for the worst case and tiles no expert uses are skipped."""
     T, width = x.shape
     top = sel.shape[1]
-    ff = w_gate_up.shape[1] // 2
+    unary = form in UNARY_FORMS
+    ff = w_gate_up.shape[1] // (1 if unary else 2)
     pairs = T * top
     max_tiles = (pairs + n_real * (MOE_TILE - 1) + MOE_TILE - 1) // MOE_TILE
     dev = x.device
@@ -1035,27 +1072,30 @@ def moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str
     st = _stream(x)
     library.check(lib.rdl_moe_align(_ptr(sel), pairs, n_real, max_tiles, _ptr(pair_slot), _ptr(slot_pair), _ptr(tile_group), st))
     xs = torch.empty((max_tiles * MOE_TILE, width), dtype=x.dtype, device=dev)
-    library.check(lib.rdl_moe_gather(_ptr(xs), _ptr(x), _ptr(slot_pair), _ptr(tile_group), max_tiles, top, width, st))
+    library.check(lib.rdl_moe_gather(_ptr(xs), _ptr(x), _ptr(slot_pair), _ptr(tile_group), _ptr(sel_w) if weights_on_input else None,
+                                     max_tiles, top, width, st))
     mid = torch.empty((max_tiles * MOE_TILE, ff), dtype=x.dtype, device=dev)
     library.check(lib.rdl_gemm_tc_grouped(_ptr(mid), _dtype_code(mid), _ptr(xs), _ptr(w_gate_up), max_tiles * MOE_TILE, ff, width, n_real,
-                                          _ptr(tile_group), 1, GATED_FORMS[form], float(param), _status(status), st))
+                                          _ptr(tile_group), 0 if unary else 1, EXPERT_FORMS[form], float(param), _status(status), st))
     y = torch.empty((max_tiles * MOE_TILE, width), dtype=x.dtype, device=dev)
     library.check(lib.rdl_gemm_tc_grouped(_ptr(y), _dtype_code(y), _ptr(mid), _ptr(w_down), max_tiles * MOE_TILE, width, ff, n_real,
                                           _ptr(tile_group), 0, 0, 0.0, _status(status), st))
     out = torch.empty_like(x)
-    library.check(lib.rdl_moe_combine(_ptr(out), _ptr(y), _ptr(x), _ptr(pair_slot), _ptr(sel_w), T, top, width, st))
+    library.check(lib.rdl_moe_combine(_ptr(out), _ptr(y), _ptr(x), _ptr(pair_slot), None if weights_on_input else _ptr(sel_w), T, top,
+                                      width, st))
     return out
 
 
-def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float) -> torch.Tensor:
+def moe_experts(x, sel, sel_w, w_gate_up, w_down, n_real: int, form: str, param: float, weights_on_input: bool = False) -> torch.Tensor:
     """The routed experts' weighted sum for every row (see `moe_experts_few` for the meaning of the arguments): with
     few pairs each streams its expert's matrices; with many, in bfloat16, the rows are sorted by expert and multiplied
     tile by tile (`moe_experts_grouped`)."""
     T, width = x.shape
     if (n_real and x.dtype is torch.bfloat16 and T * sel.shape[1] >= MOE_GROUPED_MIN_PAIRS and width % 8 == 0
-            and w_gate_up.shape[1] % 16 == 0 and x.is_contiguous() and x.data_ptr() % 16 == 0):
-        return moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
-    return moe_experts_few(x, sel, sel_w, w_gate_up, w_down, n_real, form, param)
+            and (w_gate_up.shape[1] // (1 if form in UNARY_FORMS else 2)) % 8 == 0 and w_gate_up.shape[1] % 16 == 0
+            and x.is_contiguous() and x.data_ptr() % 16 == 0):
+        return moe_experts_grouped(x, sel, sel_w, w_gate_up, w_down, n_real, form, param, weights_on_input=weights_on_input)
+    return moe_experts_few(x, sel, sel_w, w_gate_up, w_down, n_real, form, param, weights_on_input)
 
 
 # ------------------------------------------------------------------------------------------
@@ -1121,4 +1161,166 @@ def decay_attention(rows: torch.Tensor, *, q_col: int, k_col: int, v_col: int, n
         library.check(lib.rdl_decay_attention_chunked(ctypes.byref(a), _ptr(work), work.numel() * 4, _stream(rows)), 3)
     else:
         raise KernelError(f"decay_attention: unknown kind '{kind}'")
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# rows that look back along their sequence, and recurrences whose decay depends on the token
+# ------------------------------------------------------------------------------------------
+
+def norm_shift(x: torch.Tensor, weight: torch.Tensor, eps: float, shift: torch.Tensor, state: torch.Tensor, *, tok_seq, tok_pos,
+               seq_start, slots, out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """n_t = x_t / sqrt(mean(x_t^2) + eps) * weight and m_t = n_t + (n_(t-1) - n_t) * shift along each sequence, in float;
+    the row before a sequence's first row of the step comes from `state` (float32 [slots, width]; zeros at position 0),
+    which is left holding the sequence's last n.  x: float32 [rows, width].  Returns (n, m) in out_dtype."""
+    _need(x.dtype is torch.float32 and x.dim() == 2 and x.is_contiguous(), "norm_shift: contiguous float32 rows")
+    T, width = x.shape
+    _need(weight.is_contiguous() and weight.numel() == width and shift.is_contiguous() and shift.numel() == width,
+          f"norm_shift: the weight and the shift must hold {width} values")
+    _need(state.dtype is torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] == width,
+          "norm_shift: the state must be float32 [slots, width]")
+    _int32(tok_seq, "tok_seq", T); _int32(tok_pos, "tok_pos", T); _int32(seq_start, "seq_start"); _int32(slots, "slots")
+    normed = torch.empty((T, width), dtype=out_dtype, device=x.device)
+    mixed = torch.empty((T, width), dtype=out_dtype, device=x.device)
+    library.check(library.load().rdl_norm_shift(_ptr(x), _ptr(weight), _dtype_code(weight), float(eps), _ptr(shift), _dtype_code(shift),
+                                                _ptr(state), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_start), _ptr(slots), _ptr(normed),
+                                                _ptr(mixed), _dtype_code(normed), T, width, _stream(x)))
+    return normed, mixed
+
+
+SHORT_CONV_MAX_TAPS = 8
+
+
+def short_conv(rows: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], *, tok_seq,
+               tok_pos, seq_start, slots, silu: bool = True) -> torch.Tensor:
+    """Causal convolution over time per channel along each sequence, then SiLU if asked:
+    out[t, c] = act(bias[c] + sum_j weight[c, j] rows[t - (taps - 1 - j), c]), inputs before a sequence's start being zero and
+    inputs of earlier steps coming from `state` (float32 [slots, taps - 1, channels]), which is left holding the sequence's
+    last taps - 1 inputs.  rows may be a column slice of wider rows.  Returns dense [rows, channels] in the rows' dtype."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1, "short_conv: rows (or a column slice of rows)")
+    T, C = rows.shape
+    _need(weight.dim() == 2 and weight.shape[0] == C and weight.is_contiguous(), f"short_conv: the weight must be [{C}, taps]")
+    taps = weight.shape[1]
+    _need(1 <= taps <= SHORT_CONV_MAX_TAPS, f"short_conv: {taps} taps, the kernel takes 1 to {SHORT_CONV_MAX_TAPS}")
+    if bias is not None:
+        _need(bias.is_contiguous() and bias.numel() == C and bias.dtype is weight.dtype, "short_conv: the bias must match the weight")
+    if taps > 1:
+        _need(state is not None and state.dtype is torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, C),
+              "short_conv: the state must be float32 [slots, taps - 1, channels]")
+    _int32(tok_seq, "tok_seq", T); _int32(tok_pos, "tok_pos", T); _int32(seq_start, "seq_start"); _int32(slots, "slots")
+    out = torch.empty((T, C), dtype=rows.dtype, device=rows.device)
+    library.check(library.load().rdl_short_conv(_ptr(rows), rows.stride(0), _dtype_code(rows), C, taps, _ptr(weight), _dtype_code(weight),
+                                                _ptr(bias), int(bool(silu)), _ptr(state) if taps > 1 else None, _ptr(tok_seq),
+                                                _ptr(tok_pos), _ptr(seq_start), _ptr(slots), _ptr(out), T, _stream(rows)))
+    return out
+
+
+def gated_residual_add_(residual: torch.Tensor, gates: torch.Tensor, bias_a: torch.Tensor, a: torch.Tensor,
+                        bias_b: Optional[torch.Tensor] = None, b1: Optional[torch.Tensor] = None,
+                        b2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual[t, i] += sigmoid(gates[t, i] + bias_a[i]) a[t, i] + sigmoid(gates[t, width + i] + bias_b[i]) (b1[t, i] + b2[t, i]),
+    in float, in place (residual float32).  Without b1 the first term only; b2 is optional.  gates may be a column slice."""
+    _need(residual.dtype is torch.float32 and residual.is_contiguous() and residual.dim() == 2, "gated_residual_add_: float32 stream")
+    T, width = residual.shape
+    _need(gates.dim() == 2 and gates.stride(1) == 1 and gates.shape[0] == T and gates.shape[1] >= (2 if b1 is not None else 1) * width,
+          "gated_residual_add_: the gates' rows are narrower than the branches")
+    for t in (a, b1, b2):
+        if t is not None:
+            _need(tuple(t.shape) == (T, width) and t.is_contiguous() and t.dtype is gates.dtype, "gated_residual_add_: branches like the stream")
+    _need(bias_a.numel() == width and bias_a.is_contiguous(), "gated_residual_add_: a bias per column")
+    if b1 is not None:
+        _need(bias_b is not None and bias_b.numel() == width and bias_b.dtype is bias_a.dtype and bias_b.is_contiguous(),
+              "gated_residual_add_: a bias per column for the second branch")
+    _need(b2 is None or b1 is not None, "gated_residual_add_: b2 comes with b1")
+    library.check(library.load().rdl_gated_residual_add(_ptr(residual), _ptr(gates), gates.stride(0), _ptr(bias_a), _ptr(bias_b),
+                                                        _dtype_code(bias_a), _ptr(a), _ptr(b1), _ptr(b2), _dtype_code(gates), T, width,
+                                                        _stream(residual)))
+    return residual
+
+
+def _recurrence_common(a, rows, state, n_heads, n_key_heads, dim, vdim, tok_pos, seq_start, slots, n_seqs):
+    T = rows.shape[0]
+    _need(rows.dim() == 2 and rows.stride(1) == 1, "recurrence: packed rows")
+    _need(n_heads % n_key_heads == 0, f"recurrence: {n_heads} heads cannot share {n_key_heads} key heads")
+    _need(state.dtype is torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (n_heads, dim, vdim),
+          "recurrence: the state must be float32 [slots, heads, dim, vdim]")
+    _int32(tok_pos, "tok_pos", T); _int32(seq_start, "seq_start", n_seqs + 1); _int32(slots, "slots", n_seqs)
+    a.dtype, a.n_tokens, a.n_seqs, a.n_heads, a.n_key_heads, a.dim, a.vdim = _dtype_code(rows), T, n_seqs, n_heads, n_key_heads, dim, vdim
+    a.rows, a.row_stride = rows.data_ptr(), rows.stride(0)
+    a.tok_pos, a.seq_start, a.slots, a.state = tok_pos.data_ptr(), seq_start.data_ptr(), slots.data_ptr(), state.data_ptr()
+    # rows of padding sequences are not written by the kernel: they start as zeros, so that what follows sees finite numbers
+    out = torch.zeros((T, n_heads * vdim), dtype=torch.float32, device=rows.device)
+    a.out = out.data_ptr()
+    return out
+
+
+def _f32_vec(t, n, name):
+    _need(t is not None and t.dtype is torch.float32 and t.is_contiguous() and t.numel() == n, f"recurrence: {name} must be float32 [{n}]")
+    return t.data_ptr()
+
+
+def state_space_scan(rows: torch.Tensor, dt_rows: torch.Tensor, *, x_col: int, b_col: int, c_col: int, n_heads: int, n_groups: int,
+                     state_dim: int, vdim: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: Optional[torch.Tensor],
+                     state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int) -> torch.Tensor:
+    """A selective state space, token by token, in float: per head h of group g,
+    dt_t = softplus(dt_rows[t, h] + dt_bias[h]);  S_t = exp(-exp(a_log[h]) dt_t) S_(t-1) + dt_t B_t x_t^T;  y_t = S_t^T C_t + d_skip[h] x_t,
+    with x [vdim] of head h from column x_col, B and C [state_dim] of group g from b_col and c_col of `rows`, S float32
+    [slots, heads, state_dim, vdim] read from and left in `state`.  Returns float32 [tokens, heads * vdim]."""
+    a = library.RecurrenceArgs()
+    out = _recurrence_common(a, rows, state, n_heads, n_groups, state_dim, vdim, tok_pos, seq_start, slots, n_seqs)
+    T = rows.shape[0]
+    _need(rows.shape[1] >= max(x_col + n_heads * vdim, b_col + n_groups * state_dim, c_col + n_groups * state_dim),
+          "state_space_scan: the rows are narrower than the heads")
+    _need(dt_rows.dim() == 2 and dt_rows.stride(1) == 1 and tuple(dt_rows.shape) == (T, n_heads) and dt_rows.dtype is rows.dtype,
+          "state_space_scan: step sizes [tokens, heads] in the rows' dtype")
+    a.mode, a.q_col, a.k_col, a.v_col = library.REC_SSM, c_col, b_col, x_col
+    a.dt_rows, a.dt_stride = dt_rows.data_ptr(), dt_rows.stride(0)
+    a.dt_bias, a.a_log = _f32_vec(dt_bias, n_heads, "dt_bias"), _f32_vec(a_log, n_heads, "a_log")
+    a.d_skip = _f32_vec(d_skip, n_heads, "d_skip") if d_skip is not None else None
+    library.check(library.load().rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
+    return out
+
+
+def delta_prepare(rows: torch.Tensor, *, q_col: int, k_col: int, n_heads: int, n_key_heads: int, dim: int, decay_rows: torch.Tensor,
+                  beta_rows: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, q_scale: float, unit_eps: float):
+    """What enters a delta-rule recurrence, in float32: q and k of every key head as unit vectors, v / sqrt(sum(v^2) + unit_eps)
+    (q times q_scale) [tokens, key heads * dim]; decays exp(-exp(a_log[h]) softplus(decay_rows[t, h, i] + dt_bias[h, i]))
+    [tokens, heads * dim]; betas sigmoid(beta_rows[t, h]) [tokens, heads]."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[1] >= max(q_col, k_col) + n_key_heads * dim, "delta_prepare: bad rows")
+    T = rows.shape[0]
+    for t, n, name in ((decay_rows, n_heads * dim, "decay rows"), (beta_rows, n_heads, "beta rows")):
+        _need(t.dim() == 2 and t.stride(1) == 1 and tuple(t.shape) == (T, n) and t.dtype is rows.dtype, f"delta_prepare: bad {name}")
+    _need(dt_bias.is_contiguous() and dt_bias.numel() == n_heads * dim, "delta_prepare: a bias per head and key channel")
+    dev = rows.device
+    q_f = torch.empty((T, n_key_heads * dim), dtype=torch.float32, device=dev)
+    k_f = torch.empty((T, n_key_heads * dim), dtype=torch.float32, device=dev)
+    g_f = torch.empty((T, n_heads * dim), dtype=torch.float32, device=dev)
+    beta_f = torch.empty((T, n_heads), dtype=torch.float32, device=dev)
+    a = library.DeltaPrepareArgs()
+    a.dtype, a.bias_dtype, a.n_tokens, a.n_heads, a.n_key_heads, a.dim = _dtype_code(rows), _dtype_code(dt_bias), T, n_heads, n_key_heads, dim
+    a.rows, a.row_stride, a.q_col, a.k_col = rows.data_ptr(), rows.stride(0), q_col, k_col
+    a.decay_rows, a.decay_stride = decay_rows.data_ptr(), decay_rows.stride(0)
+    a.beta_rows, a.beta_stride = beta_rows.data_ptr(), beta_rows.stride(0)
+    a.dt_bias, a.a_log = dt_bias.data_ptr(), _f32_vec(a_log, n_heads, "a_log")
+    a.q_scale, a.unit_eps = float(q_scale), float(unit_eps)
+    a.q_f, a.k_f, a.g_f, a.beta_f = q_f.data_ptr(), k_f.data_ptr(), g_f.data_ptr(), beta_f.data_ptr()
+    library.check(library.load().rdl_delta_prepare(ctypes.byref(a), _stream(rows)))
+    return q_f, k_f, g_f, beta_f
+
+
+def delta_rule_scan(rows: torch.Tensor, *, v_col: int, q_f, k_f, g_f, beta_f, n_heads: int, n_key_heads: int, dim: int, vdim: int,
+                    state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int) -> torch.Tensor:
+    """The delta rule with a decay per key channel, token by token, in float: per head h with key head j(h),
+    S <- g_t (.) S (row i times g_t[i]);  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t,
+    v [vdim] of head h from column v_col of `rows`, the rest as `delta_prepare` made it; S float32 [slots, heads, dim, vdim]
+    read from and left in `state`.  Returns float32 [tokens, heads * vdim]."""
+    a = library.RecurrenceArgs()
+    out = _recurrence_common(a, rows, state, n_heads, n_key_heads, dim, vdim, tok_pos, seq_start, slots, n_seqs)
+    T = rows.shape[0]
+    _need(rows.shape[1] >= v_col + n_heads * vdim, "delta_rule_scan: the rows are narrower than the heads")
+    for t, n, name in ((q_f, n_key_heads * dim, "q"), (k_f, n_key_heads * dim, "k"), (g_f, n_heads * dim, "decays"), (beta_f, n_heads, "betas")):
+        _need(t.dtype is torch.float32 and t.is_contiguous() and tuple(t.shape) == (T, n), f"delta_rule_scan: {name} must be float32 [{T}, {n}]")
+    a.mode, a.v_col = library.REC_DELTA, v_col
+    a.q_f, a.k_f, a.g_f, a.beta_f = q_f.data_ptr(), k_f.data_ptr(), g_f.data_ptr(), beta_f.data_ptr()
+    library.check(library.load().rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
     return out

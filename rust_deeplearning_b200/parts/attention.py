@@ -16,6 +16,11 @@ Optional parameters, for designs that have them (the reference's attention has n
   sinks        a learned logit per query head without key or value: exp(sink_h) joins the softmax's denominator once
   gate         "sigmoid": the concatenated heads are multiplied element by element by sigmoid(W_g x) before W_o
   value_dim    values of another size than keys
+  score_bias   no softmax: the weight of a visible key is sigmoid(score + score_bias[h]), a learned number per query head,
+               and the weights are not normalised over the keys
+  cache_window the keys the cache keeps per sequence where later runs that read this run's keys look further back than
+               this run's own window (default: the window; "all": every key)
+A run that reads another run's keys and values is built without wk and wv.
 With any of them the mixer makes q, k, v and the gate's logits in one product and takes `ops.rope_norm_cache`
 (rotation, head norm and cache write in one pass, rounded once) in place of `ops.rope_cache`.  Keys and values of
 different sizes share the attention kernels by zero padding: the heads of q, k, v and of the gate are all laid out
@@ -41,23 +46,48 @@ class Attention:
     query_tile_rows = ops.PREFILL_QUERY_TILE
 
     def __init__(self, *, hidden_size, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, position,
-                 wq, wk, wv, wo, value_dim=None, qk_norm_eps=None, sinks=None, gate=None, wg=None):
+                 wq, wk, wv, wo, value_dim=None, qk_norm_eps=None, sinks=None, gate=None, wg=None, score_bias=None,
+                 cache_window=None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
         value_dim = head_dim if value_dim is None else value_dim
-        self.extended = (value_dim != head_dim or qk_norm_eps is not None or sinks is not None or gate is not None)
+        if window is None or cache_window == "all":
+            self.cache_window = None
+        else:
+            self.cache_window = window if cache_window is None else int(cache_window)
+            if self.cache_window < window:
+                raise ValueError(f"attention: the cache keeps {self.cache_window} keys, the window spans {window}")
+        if score_bias is not None and (sinks is not None or qk_norm_eps is not None or gate is not None):
+            raise ValueError("attention: sigmoid weights come without sinks, head norms or an output gate")
+        if score_bias is not None and score_bias.numel() != n_heads:
+            raise ValueError(f"attention: {score_bias.numel()} score biases for {n_heads} heads")
+        self.score_bias = score_bias.to(torch.float32).contiguous() if score_bias is not None else None
+        self.extended = qk_norm_eps is not None or sinks is not None or gate is not None or (value_dim != head_dim and score_bias is None)
         if self.extended:
             self._init_extended(hidden_size, n_heads, n_kv_heads, head_dim, value_dim, score_scale, softcap, window, position,
                                 wq, wk, wv, wo, qk_norm_eps, sinks, gate, wg)
             return
-        if wv.shape[0] != wk.shape[0]:
-            raise ValueError("this attention's kernels take key and value rows of one size")
+        if (wk is None) != (wv is None):
+            raise ValueError("attention: keys and values come together or not at all")
+        if value_dim != head_dim:
+            # keys and values of different sizes share the kernels by zero padding: every head is laid out with
+            # max(head_dim, value_dim) values (zero rows of the products' matrices, zero columns of W_o)
+            D = max(head_dim, value_dim)
+            wq = _pad_heads(wq, n_heads, head_dim, D)
+            if wk is not None:
+                wk, wv = _pad_heads(wk, n_kv_heads, head_dim, D), _pad_heads(wv, n_kv_heads, value_dim, D)
+            if value_dim != D:
+                w = torch.zeros((wo.shape[0], n_heads, D), dtype=wo.dtype, device=wo.device)
+                w[:, :, :value_dim] = wo.view(wo.shape[0], n_heads, value_dim)
+                wo = w.view(wo.shape[0], n_heads * D).contiguous()
+            head_dim = D
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
         self.score_scale, self.softcap, self.window = float(score_scale), softcap, window
         self.position = position
         # one product for q, k and v: rows of the three matrices one after another
-        self.w_qkv = torch.cat([wq, wk, wv], dim=0).contiguous()
+        self.w_qkv = torch.cat([wq, wk, wv], dim=0).contiguous() if wk is not None else wq.contiguous()
         self.w_q = self.w_qkv[: n_heads * head_dim]       # view, for runs that read another run's cache
+        self.has_kv = wk is not None
         self.w_o = wo
         self.q_width = n_heads * head_dim
         self.kv_width = n_kv_heads * head_dim
@@ -138,7 +168,7 @@ class Attention:
         return ops.linear(ctx, self.w_o)
 
     def needs(self):
-        return KVRequirement(self.n_kv_heads, self.head_dim, self.window), None
+        return KVRequirement(self.n_kv_heads, self.head_dim, self.cache_window), None
 
     def _pages(self, batch, cache: RunCache) -> Optional[ops.KVPages]:
         if cache.k is None:
@@ -159,11 +189,14 @@ class Attention:
             return self._forward_extended(x, batch, cache)
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
-        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
+        # sigmoid weights: the plain kernel, which forms every score and weight in float
+        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256 and self.score_bias is None
         fast_decode = fast and nh // nkv <= 8 and cache.page_size % 16 == 0 and cache.page_size <= 64
         common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale,
-                      softcap=self.softcap, window=self.window)
+                      softcap=self.softcap, window=self.window, sigmoid_bias=self.score_bias)
         tables, rotary_dim = self._rotary_tables()
+        if cache.owns_kv and not self.has_kv:
+            raise ValueError("attention: a run without key and value projections must read another run's cache")
 
         if not cache.owns_kv:
             # queries only; keys and values are those of another run of this step
@@ -242,6 +275,15 @@ class Attention:
         return ops.linear_branch(ctx, self.w_o, sink)
 
 
+def _pad_heads(w, n, d, D):
+    """[n * d, in] -> [n * D, in]: every head's rows followed by zero rows."""
+    if d == D:
+        return w
+    out = torch.zeros((n, D, w.shape[1]), dtype=w.dtype, device=w.device)
+    out[:, :d] = w.view(n, d, w.shape[1])
+    return out.view(n * D, w.shape[1])
+
+
 def cache_owner(batch, run: int) -> int:
     return batch.cache_owner_of[run]
 
@@ -252,7 +294,9 @@ def _build_attention(spec: PartSpec, ctx: BuildContext) -> Attention:
     return Attention(hidden_size=p["hidden_size"], n_heads=p["n_heads"], n_kv_heads=p["n_kv_heads"],
                      head_dim=p["head_dim"], score_scale=p["score_scale"], softcap=p.get("softcap"),
                      window=p.get("window"), position=position,
-                     wq=ctx.tensor(t["q"]), wk=ctx.tensor(t["k"]), wv=ctx.tensor(t["v"]), wo=ctx.tensor(t["o"]),
+                     wq=ctx.tensor(t["q"]), wk=ctx.tensor(t["k"]) if "k" in t else None,
+                     wv=ctx.tensor(t["v"]) if "v" in t else None, wo=ctx.tensor(t["o"]),
+                     score_bias=ctx.tensor(t["score_bias"]) if "score_bias" in t else None, cache_window=p.get("cache_window"),
                      value_dim=p.get("value_dim"), qk_norm_eps=p.get("qk_norm_eps"),
                      sinks=ctx.tensor(t["sinks"]) if "sinks" in t else None, gate=p.get("gate"),
                      wg=ctx.tensor(t["g"]) if "g" in t else None)

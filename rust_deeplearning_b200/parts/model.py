@@ -22,7 +22,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..cache.cache import RunNeeds
+from ..cache.cache import RunNeeds, StateRequirement
 from ..kernels import ops
 from .norm import ResidualStream
 from .registry import BuildContext, build_part, register_part
@@ -147,6 +147,87 @@ def _build_postnorm(layer: LayerSpec, ctx: BuildContext) -> PostNormBlock:
 register_part("block", "postnorm", _build_postnorm, replace=True)
 
 
+class ParallelBlock:
+    """One norm whose output both sublayers read, and one sum:
+        n = norm(x);   x <- x + c1 * mixer(m) + c2 * ff(n)
+    with two optional mechanisms, each a parameter of the arrangement (`LayerSpec.params`):
+      token_shift      m_t = n_t + (n_(t-1) - n_t) * shift, element by element, n_(-1) = 0: the mixer reads every row moved
+                       towards the row before it along its sequence (the feed-forward reads n as it is).  The sequence's
+                       last n is state the block keeps per slot, beside the mixer's own (`needs()`); tensor role "shift".
+      gated_residual   c1 = sigmoid(R1 n + b1), c2 = sigmoid(R2 n + b2), element by element (c = 1 without it); tensor
+                       roles "gate_mixer", "gate_mixer_bias", "gate_ff", "gate_ff_bias".  Both gates are one product.
+    The norm, the shift, the gates' sigmoids and the sum run in float32 on the stream (one kernel before the sublayers,
+    one after).  A feed-forward that keeps parts of its result apart (`forward_parts`) has them added in that last kernel.
+    A layer without a feed-forward has the mixer's branch only."""
+
+    def __init__(self, mixer, feed_forward, norm, act_dtype: torch.dtype, hidden_size: int, shift, gates):
+        self.mixer, self.feed_forward, self.norm, self.act_dtype, self.hidden_size = mixer, feed_forward, norm, act_dtype, hidden_size
+        if not callable(getattr(norm, "fused_params", None)) or norm.fused_params().offset != 0.0:
+            raise ValueError("parallel block: the norm must be a scale-only root-mean-square norm without an offset")
+        self.shift = shift
+        self.w_gates = self.b_mixer = self.b_ff = None
+        if gates is not None:
+            w1, b1, w2, b2 = gates
+            self.w_gates = torch.cat([w1, w2], dim=0).contiguous() if feed_forward is not None else w1.contiguous()
+            self.b_mixer, self.b_ff = b1.contiguous(), (b2.contiguous() if feed_forward is not None else None)
+        kv, state = mixer.needs()
+        self._mixer_state = state
+        own = (StateRequirement((hidden_size,), "float32"),) if shift is not None else ()
+        mixer_states = () if state is None else (tuple(state) if isinstance(state, (tuple, list)) else (state,))
+        self._needs = (kv, own + mixer_states if (own or mixer_states) else None)
+
+    first_norm = None       # the norm is part of a kernel of the block's own
+
+    def needs(self):
+        return self._needs
+
+    def _mixer_cache(self, cache):
+        """The run's cache as the mixer declared it: its own state tensors without the block's."""
+        if self._mixer_state is None:
+            return cache._replace(state=None)
+        rest = cache.state[1 if self.shift is not None else 0:]
+        return cache._replace(state=rest if isinstance(self._mixer_state, (tuple, list)) else rest[0])
+
+    def forward(self, stream: ResidualStream, batch, cache, run: int):
+        stream.norm_after_block = None
+        x = stream.writable()
+        p = self.norm.fused_params()
+        if self.shift is not None:
+            n, m = ops.norm_shift(x, p.weight, p.eps, self.shift, cache.state[0], tok_seq=batch.tok_seq, tok_pos=batch.tok_pos,
+                                  seq_start=batch.seq_start, slots=batch.slots, out_dtype=self.act_dtype)
+        else:
+            n = m = self.norm.apply(x, self.act_dtype)
+        a = self.mixer.forward(m, batch, self._mixer_cache(cache), run)
+        f1 = f2 = None
+        if self.feed_forward is not None:
+            if hasattr(self.feed_forward, "forward_parts"):
+                f1, f2 = self.feed_forward.forward_parts(n)
+            else:
+                f1 = self.feed_forward.forward(n)
+        if self.w_gates is not None:
+            ops.gated_residual_add_(x, ops.linear(n, self.w_gates), self.b_mixer, a, self.b_ff, f1, f2)
+        else:
+            for branch in (a, f1, f2):
+                if branch is not None:
+                    ops.residual_add_(x, branch)
+
+
+def _build_parallel(layer: LayerSpec, ctx: BuildContext) -> ParallelBlock:
+    mixer = build_part("mixer", layer.mixer, ctx)
+    ff = build_part("feed_forward", layer.feed_forward, ctx) if layer.feed_forward is not None else None
+    norm = build_part("norm", layer.norms["pre"], ctx)
+    t = layer.tensors
+    shift = ctx.tensor(t["shift"]) if layer.params.get("token_shift") else None
+    gates = None
+    if layer.params.get("gated_residual"):
+        gates = (ctx.tensor(t["gate_mixer"]), ctx.tensor(t["gate_mixer_bias"]),
+                 ctx.tensor(t["gate_ff"]) if ff is not None else None, ctx.tensor(t["gate_ff_bias"]) if ff is not None else None)
+    return ParallelBlock(mixer, ff, norm, ctx.dtype, layer.params["hidden_size"], shift, gates)
+
+
+register_part("block", "parallel", _build_parallel, replace=True)
+
+
 class Model:
     """A model built from a ModelSpec and loaded tensors.  Nothing here names an architecture."""
 
@@ -164,6 +245,9 @@ class Model:
                 for t in p.tensors.values():
                     if t.name not in keep:
                         weights.pop(t.name, None)
+            for t in layer.tensors.values():
+                if t.name not in keep:
+                    weights.pop(t.name, None)
         self.final_norm = build_part("norm", spec.final_norm, ctx)
         self.head = build_part("head", spec.head, ctx)
         self.schedule = list(spec.schedule)
@@ -189,7 +273,9 @@ class Model:
         """What each schedule entry needs of the cache."""
         out = []
         for s in self.schedule:
-            kv, state = self.layers[s.layer].mixer.needs()
+            block = self.layers[s.layer]
+            # a block that keeps state of its own beside its mixer's says so itself
+            kv, state = block.needs() if callable(getattr(block, "needs", None)) else block.mixer.needs()
             out.append(RunNeeds(kv, state, s.reads_cache_of))
         return out
 

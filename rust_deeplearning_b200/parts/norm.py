@@ -190,6 +190,13 @@ class ResidualStream:
         self._flush()
         return self.x
 
+    def writable(self) -> torch.Tensor:
+        """x itself, for a block that forms its sum in place with a kernel of its own; copies derived from x are dropped."""
+        self._settled()
+        self._flush()
+        self._rows = self._operand = None
+        return self.x
+
     # ---- norm after the sum ----
     def rows(self, dtype: torch.dtype) -> torch.Tensor:
         """The stream itself as a part's input: x for float32, else x converted (the copy `renorm` made, if x has not

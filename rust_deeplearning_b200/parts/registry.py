@@ -12,7 +12,7 @@ from typing import Any, Callable, Dict
 
 import torch
 
-from .spec import PartSpec, TensorSpec
+from .spec import PartSpec, TensorSpec, shape_fits
 
 ROLES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 _REGISTRY: Dict[str, Dict[str, Callable]] = {r: {} for r in ROLES}
@@ -50,7 +50,7 @@ class BuildContext:
             w = self.weights[t.name]
         except KeyError:
             raise PartError(f"tensor '{t.name}' was not loaded") from None
-        if tuple(w.shape) != tuple(t.shape):
+        if not shape_fits(tuple(w.shape), tuple(t.shape)):
             raise PartError(f"tensor '{t.name}' has shape {tuple(w.shape)}, expected {tuple(t.shape)}")
         return w
 

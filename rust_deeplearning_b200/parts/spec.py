@@ -22,12 +22,19 @@ class TensorSpec:
                       the compute dtype
           "int"     - integer table, kept as int32
     init_std, init_mean: standard deviation and mean used by the random-weights mode.
+    A size of None in `shape` is one that only the file gives (a low rank the configuration does not name): any
+    size passes the checks there, and the random-weights mode, which needs a number, refuses the tensor.
     """
     name: str
-    shape: Tuple[int, ...]
+    shape: Tuple[Optional[int], ...]
     kind: str = "matrix"
     init_std: float = 0.02
     init_mean: float = 0.0
+
+
+def shape_fits(got, want) -> bool:
+    """Whether a tensor's shape is the described one (None in the description: any size)."""
+    return len(got) == len(want) and all(w is None or int(g) == int(w) for g, w in zip(got, want))
 
 
 @dataclass(frozen=True)
@@ -53,6 +60,7 @@ class LayerSpec:
     feed_forward: Optional[PartSpec]      # None: the layer has a mixer only
     norms: Dict[str, PartSpec]
     params: Dict[str, Any] = field(default_factory=dict)     # constants of the arrangement itself (a post-norm block's alpha)
+    tensors: Dict[str, TensorSpec] = field(default_factory=dict)   # tensors of the arrangement itself, by role (gates on its branches)
 
 
 @dataclass(frozen=True)
@@ -89,6 +97,8 @@ class ModelSpec:
                 yield from layer.feed_forward.walk()
             for n in layer.norms.values():
                 yield n
+            if layer.tensors:
+                yield PartSpec("block_tensors", {}, layer.tensors)
         yield self.final_norm
         yield self.head
 

@@ -15,7 +15,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..parts.spec import ModelSpec, TensorSpec
+from ..parts.spec import ModelSpec, TensorSpec, shape_fits
 from . import counter_random
 from .safetensors_io import WeightFiles
 
@@ -71,7 +71,7 @@ def check_weights(spec: ModelSpec, files, where: str, strict: bool = True) -> No
         if name not in have:
             continue
         file_dtype, shape = files.info(name)
-        if tuple(shape) != tuple(t.shape):
+        if not shape_fits(tuple(shape), tuple(t.shape)):
             wrong_shape.append((name, t.shape, shape))
         allowed = _INT_FILE_DTYPES if t.kind == "int" else _FLOAT_FILE_DTYPES
         if file_dtype not in allowed:
@@ -99,6 +99,8 @@ def random_tensor(t: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") ->
     The reference's random models are unseeded (`rustml/core/main/src/core/tensor/tensor.rs:217-238`)."""
     if t.kind == "int":
         raise ValueError(f"no random initialisation for integer table '{t.name}'")
+    if any(d is None for d in t.shape):
+        raise ValueError(f"tensor '{t.name}' has a size that only a weight file gives; name it in the configuration to make random weights")
     key = counter_random.tensor_key(seed, t.name)
     n = 1
     for d in t.shape:
