@@ -296,14 +296,20 @@ def _check_kv_from(i: int, layer: RevepelLayer, layers) -> List[str]:
 
 # ---- the description as parts ----
 
+def _mat(name: str, out_features, in_features) -> TensorSpec:
+    """A matrix [out, in]; random weights are drawn with a standard deviation of in^(-1/2), so that a product keeps the
+    size of what it reads and every mechanism of a random model weighs in the logits."""
+    return TensorSpec(name, (out_features, in_features), init_std=float(in_features or 16) ** -0.5)
+
+
 def _state_space_part(cfg: RevepelConfig, m: StateSpaceConfig, p: str) -> PartSpec:
     W, inner, gn = cfg.width, m.heads * m.vdim, m.groups * m.state
     channels = inner + 2 * gn
     vec = lambda name, n, std, mean=0.0: TensorSpec(p + name, (n,), "vector", init_std=std, init_mean=mean)
-    tensors = {"in": TensorSpec(p + "in", (2 * inner + 2 * gn + m.heads, W)),
+    tensors = {"in": _mat(p + "in", 2 * inner + 2 * gn + m.heads, W),
                "conv": TensorSpec(p + "conv", (channels, m.conv), init_std=0.4), "conv_bias": vec("conv.b", channels, 0.1),
                "dt_bias": vec("dt_bias", m.heads, 0.5), "a_log": vec("A_log", m.heads, 0.5), "d_skip": vec("D", m.heads, 0.2, 1.0),
-               "norm": vec("norm", inner, 0.1, 1.0), "o": TensorSpec(p + "o", (W, inner))}
+               "norm": vec("norm", inner, 0.1, 1.0), "o": _mat(p + "o", W, inner)}
     return PartSpec("state_space", {"hidden_size": W, "n_heads": m.heads, "vdim": m.vdim, "state_dim": m.state, "n_groups": m.groups,
                                     "taps": m.conv, "norm_groups": m.norm_groups, "eps": cfg.eps}, tensors)
 
@@ -311,26 +317,26 @@ def _state_space_part(cfg: RevepelConfig, m: StateSpaceConfig, p: str) -> PartSp
 def _delta_part(cfg: RevepelConfig, m: DeltaConfig, p: str) -> PartSpec:
     W, H, J, d, e = cfg.width, m.heads, m.kv_heads, m.dim, m.vdim
     conv = lambda name, n: TensorSpec(p + name, (n, m.conv), init_std=0.4)
-    tensors = {"q": TensorSpec(p + "q", (J * d, W)), "k": TensorSpec(p + "k", (J * d, W)), "v": TensorSpec(p + "v", (H * e, W)),
+    tensors = {"q": _mat(p + "q", J * d, W), "k": _mat(p + "k", J * d, W), "v": _mat(p + "v", H * e, W),
                "conv_q": conv("q.conv", J * d), "conv_k": conv("k.conv", J * d), "conv_v": conv("v.conv", H * e),
-               "beta": TensorSpec(p + "b", (H, W)),
+               "beta": _mat(p + "b", H, W),
                "a_log": TensorSpec(p + "A_log", (H,), "vector", init_std=0.5),
                "norm": TensorSpec(p + "norm", (e,), "vector", init_std=0.1, init_mean=1.0),
-               "decay_down": TensorSpec(p + "a1", (m.decay_rank, W)), "decay_up": TensorSpec(p + "a2", (H * d, m.decay_rank), init_std=0.1),
+               "decay_down": _mat(p + "a1", m.decay_rank, W), "decay_up": TensorSpec(p + "a2", (H * d, m.decay_rank), init_std=0.1),
                "dt_bias": TensorSpec(p + "dt_bias", (H * d,), "vector", init_std=0.5),
-               "gate_down": TensorSpec(p + "g1", (m.gate_rank, W)), "gate_up": TensorSpec(p + "g2", (H * e, m.gate_rank), init_std=0.1),
-               "o": TensorSpec(p + "o", (W, H * e))}
+               "gate_down": _mat(p + "g1", m.gate_rank, W), "gate_up": TensorSpec(p + "g2", (H * e, m.gate_rank), init_std=0.1),
+               "o": _mat(p + "o", W, H * e)}
     return PartSpec("delta_rule", {"hidden_size": W, "n_heads": H, "n_key_heads": J, "dim": d, "vdim": e, "taps": m.conv, "eps": cfg.eps,
                                    "unit_eps": UNIT_EPS, "q_scale": d ** -0.5}, tensors)
 
 
 def _attention_part(cfg: RevepelConfig, m: AttentionConfig, p: str, cache_window) -> PartSpec:
     W, H, G = cfg.width, m.heads, m.kv_heads
-    tensors = {"q": TensorSpec(p + "q", (H * m.dim, W)), "o": TensorSpec(p + "o", (W, H * m.vdim)),
+    tensors = {"q": _mat(p + "q", H * m.dim, W), "o": _mat(p + "o", W, H * m.vdim),
                "score_bias": TensorSpec(p + "pb", (H,), "vector", init_std=1.0, init_mean=-3.0)}
     if m.kv_from is None:
-        tensors["k"] = TensorSpec(p + "k", (G * m.dim, W))
-        tensors["v"] = TensorSpec(p + "v", (G * m.vdim, W))
+        tensors["k"] = _mat(p + "k", G * m.dim, W)
+        tensors["v"] = _mat(p + "v", G * m.vdim, W)
     position = None
     if m.rot is not None:
         scaling = dict(m.rot.scaling, kind="yarn") if m.rot.scaling is not None else None
@@ -343,13 +349,13 @@ def _attention_part(cfg: RevepelConfig, m: AttentionConfig, p: str, cache_window
 
 def _moe_part(cfg: RevepelConfig, f: MoEConfig, p: str) -> PartSpec:
     W = cfg.width
-    tensors = {"router": TensorSpec(p + "router", (f.experts, W), init_std=0.1)}
+    tensors = {"router": _mat(p + "router", f.experts, W)}
     for e in range(f.experts):
-        tensors[f"up{e}"] = TensorSpec(p + f"e{e}.up", (f.ff, W))
-        tensors[f"down{e}"] = TensorSpec(p + f"e{e}.down", (W, f.ff))
+        tensors[f"up{e}"] = _mat(p + f"e{e}.up", f.ff, W)
+        tensors[f"down{e}"] = _mat(p + f"e{e}.down", W, f.ff)
     if f.shared_ff is not None:
-        tensors["shared_up"] = TensorSpec(p + "shared.up", (f.shared_ff, W))
-        tensors["shared_down"] = TensorSpec(p + "shared.down", (W, f.shared_ff))
+        tensors["shared_up"] = _mat(p + "shared.up", f.shared_ff, W)
+        tensors["shared_down"] = _mat(p + "shared.down", W, f.shared_ff)
     return PartSpec("routed_experts", {"hidden_size": W, "expert_size": f.ff, "n_experts": f.experts, "n_identity": 0, "top": f.top,
                                        "form": "relu2", "scoring": "sigmoid", "weights_on_input": True}, tensors)
 
@@ -386,11 +392,11 @@ def build_spec(cfg: RevepelConfig) -> ModelSpec:
             mixer = _attention_part(cfg, layer.mixer, p + "mix.", "all" if (keep is None and layer.mixer.window is not None) else keep)
             reads = layer.mixer.kv_from
         tensors = {"shift": TensorSpec(p + "shift", (W,), "vector", init_std=0.2, init_mean=0.5),
-                   "gate_mixer": TensorSpec(p + "rg1", (W, W)), "gate_mixer_bias": TensorSpec(p + "rg1.b", (W,), "vector", init_std=0.5)}
+                   "gate_mixer": _mat(p + "rg1", W, W), "gate_mixer_bias": TensorSpec(p + "rg1.b", (W,), "vector", init_std=0.5)}
         ff = None
         if layer.mlp is not None:
             ff = _moe_part(cfg, layer.mlp, p + "mlp.")
-            tensors["gate_ff"] = TensorSpec(p + "rg2", (W, W))
+            tensors["gate_ff"] = _mat(p + "rg2", W, W)
             tensors["gate_ff_bias"] = TensorSpec(p + "rg2.b", (W,), "vector", init_std=0.5)
         layers.append(LayerSpec("parallel", mixer, ff, {"pre": norm(p + "norm1")},
                                 {"hidden_size": W, "token_shift": True, "gated_residual": True}, tensors))
@@ -402,7 +408,7 @@ def build_spec(cfg: RevepelConfig) -> ModelSpec:
                            {"table": TensorSpec("embed", (V, W), init_std=0.05)}),
         layers=tuple(layers), schedule=tuple(schedule), final_norm=norm("final.norm"),
         head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": W, "softcap": None, "scale": cfg.logit_scale},
-                      {"weight": TensorSpec("head", (V, W))}),
+                      {"weight": _mat("head", V, W)}),
         ignored_tensors=tuple(f"l{i}.rg2*" for i, layer in enumerate(cfg.layers) if layer.mlp is None))
     spec.validate()
     return spec

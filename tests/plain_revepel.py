@@ -149,9 +149,11 @@ def rotary_angles(rot):
 
 
 def turn(vec, pos, rot):
-    n = rot["dims"]
-    f, mag = rotary_angles(rot)
     out = np.array(vec, dtype=np.float64)
+    if not rot:
+        return out
+    f, mag = rotary_angles(rot)
+    n = rot["dims"]
     for i in range(n // 2):
         c, s = math.cos(pos * f[i]) * mag, math.sin(pos * f[i]) * mag
         u, v = vec[i], vec[i + n // 2]
@@ -164,7 +166,7 @@ def keys_values(w, p, m, h):
     T, J, d, e = h.shape[0], m["kv_heads"], m["dim"], m["vdim"]
     k = (h @ w[p + "k"].T).reshape(T, J, d)
     v = (h @ w[p + "v"].T).reshape(T, J, e)
-    k = np.stack([np.stack([turn(k[t, j], t, m["rot"]) for j in range(J)]) for t in range(T)])
+    k = np.stack([np.stack([turn(k[t, j], t, m.get("rot")) for j in range(J)]) for t in range(T)])
     return k, v
 
 
@@ -175,8 +177,9 @@ def sigmoid_attention(w, p, m, h, k, v):
     for t in range(T):
         for a in range(H):
             j = a // (H // J)
-            qa = turn(q[t, a], t, m["rot"])
-            for s in range(max(0, t - m["mask"]["size"] + 1), t + 1):
+            qa = turn(q[t, a], t, m.get("rot"))
+            first = 0 if not m.get("mask") else max(0, t - m["mask"]["size"] + 1)
+            for s in range(first, t + 1):
                 out[t, a] += sigmoid(float(qa @ k[s, j]) * m["scale"] + w[p + "pb"][a]) * v[s, j]
     return out.reshape(T, H * e) @ w[p + "o"].T
 
@@ -191,13 +194,21 @@ def two_matrix(w, p, h):
     return relu2(h @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def routed(w, p, f, h):
+def routed(w, p, f, h, margins=None):
+    """margins: a list that receives, per token, the gap between the last chosen score and the best one left out
+    (infinite where every expert is chosen): a choice with a small gap may flip between number formats."""
     E, top = f["router"]["experts"], f["router"]["top"]
     out = np.zeros_like(h)
+    gaps = np.full(h.shape[0], np.inf)
     for t in range(h.shape[0]):
         s = sigmoid(w[p + "router"] @ h[t])
-        for e in np.argsort(-s, kind="stable")[:top]:
+        order = np.argsort(-s, kind="stable")
+        if top < E:
+            gaps[t] = s[order[top - 1]] - s[order[top]]
+        for e in order[:top]:
             out[t] += two_matrix(w, f"{p}e{e}.", (s[e] * h[t])[None])[0]
+    if margins is not None:
+        margins.append(gaps)
     if f.get("shared"):
         out += two_matrix(w, p + "shared.", h)
     return out
@@ -205,8 +216,9 @@ def routed(w, p, f, h):
 
 # ---- the model ----
 
-def forward(cfg, w, ids, layers_out=None):
-    """float64 logits [T, vocab]; layers_out: a list that receives the stream after every layer."""
+def forward(cfg, w, ids, layers_out=None, margins=None):
+    """float64 logits [T, vocab]; layers_out: a list that receives the stream after every layer; margins: a list that
+    receives every routed layer's gaps (see `routed`)."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][np.asarray(ids)] * cfg["embedding"]["scale"]
     kept = {}
@@ -225,7 +237,7 @@ def forward(cfg, w, ids, layers_out=None):
             a = sigmoid_attention(w, p + "mix.", m, mixed, k, v)
         branch = sigmoid(n @ w[p + "rg1"].T + w[p + "rg1.b"]) * a
         if layer.get("mlp") is not None:
-            branch = branch + sigmoid(n @ w[p + "rg2"].T + w[p + "rg2.b"]) * routed(w, p + "mlp.", layer["mlp"], n)
+            branch = branch + sigmoid(n @ w[p + "rg2"].T + w[p + "rg2.b"]) * routed(w, p + "mlp.", layer["mlp"], n, margins)
         x = x + branch
         if layers_out is not None:
             layers_out.append(x.copy())
