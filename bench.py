@@ -268,6 +268,29 @@ def dokulorn_shape(width, heads, kv_heads, dim, ff, layers, vocab):
             "embedding": {"scale": 10.0}, "max_positions": CONTEXT, "layers": out}
 
 
+def revepel_shape(width, ssm_heads, state, heads, kv_heads, dim, window, experts, top, ff, shared_ff, layers, vocab, rank=64):
+    """A Revepel configuration of `layers` layers in the order state space, delta rule, attention, attention on the keys of
+    the layer before it; every layer with routed two-matrix experts and a shared one."""
+    rot = {"base": 10000.0, "dims": dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            layer = {"type": "mamba2", "mixer": {"heads": ssm_heads, "vdim": width // ssm_heads, "state": state, "groups": 1, "norm_groups": 1, "conv": 4}}
+        elif kind == 1:
+            layer = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4,
+                                                        "decay_rank": rank, "gate_rank": rank}}
+        else:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window}, "rot": rot}
+            if kind == 3:
+                m["kv_from"] = i - 1
+            layer = {"type": "attention", "mixer": m}
+        out.append(dict(layer, mlp=mlp))
+    return {"architecture": "Revepel", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": 10.0}, "logit_scale": 1.0,
+            "max_positions": CONTEXT, "layers": out}
+
+
 DESIGN_SIZES = {
     # name: (the design's arguments, the Gemma 2 arguments of equal width / heads / active feed-forward width)
     "w1024": (dict(width=1024, heads=8, dim=64, rot_dim=64, vdim=128, kv_rank=192, window=1024, experts=16, identity=2, top=2, ff=1024,
@@ -285,8 +308,23 @@ DOKULORN_SIZES = {
     "w2048": (dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, layers=4, vocab=32000),
               dict(width=2048, heads=16, kv_heads=8, head_dim=128, intermediate=8192, window=CONTEXT, layers=4, vocab=32000)),
 }
-DESIGNS = {"ligirax": (ligirax_shape, DESIGN_SIZES, "ligirax beside gemma2 at equal width, heads and active feed-forward width"),
-           "dokulorn": (dokulorn_shape, DOKULORN_SIZES, "dokulorn beside gemma2 at equal width, heads, head size and feed-forward width")}
+REVEPEL_SIZES = {
+    # four layers each (state space, delta rule, attention, attention on shared keys), every layer with routed experts whose
+    # active width (top x ff + shared) is Dokulorn's dense width; Dokulorn, the closest registered design (state of fixed size
+    # beside keys and values), with the same width, heads, head size and feed-forward width
+    "w1024": (dict(width=1024, ssm_heads=16, state=128, heads=8, kv_heads=4, dim=128, window=1024, experts=16, top=2, ff=1024,
+                   shared_ff=2048, layers=4, vocab=32000),
+              dict(width=1024, heads=8, kv_heads=4, dim=128, ff=4096, layers=4, vocab=32000)),
+    "w2048": (dict(width=2048, ssm_heads=32, state=128, heads=16, kv_heads=8, dim=128, window=4096, experts=32, top=4, ff=1024,
+                   shared_ff=4096, layers=4, vocab=32000),
+              dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, layers=4, vocab=32000)),
+}
+# design -> (its shape, its sizes, the title, the registered design it stands beside and that design's shape)
+DESIGNS = {"ligirax": (ligirax_shape, DESIGN_SIZES, "ligirax beside gemma2 at equal width, heads and active feed-forward width", "gemma2", gemma_like),
+           "dokulorn": (dokulorn_shape, DOKULORN_SIZES, "dokulorn beside gemma2 at equal width, heads, head size and feed-forward width", "gemma2",
+                        gemma_like),
+           "revepel": (revepel_shape, REVEPEL_SIZES, "revepel beside dokulorn at equal width, heads, head size and active feed-forward width",
+                       "dokulorn", dokulorn_shape)}
 
 
 def design_point(cfg, vocab, torch, rng, steps, warmup, prompt_len, batches, long_prompt=CONTEXT):
@@ -351,14 +389,14 @@ def design_comparison(args):
     clocks = ClockSampler()
     clocks.start()
     sizes = {}
-    shape_of, table, title = DESIGNS[args.design]
+    shape_of, table, title, beside, beside_shape = DESIGNS[args.design]
     for name, (lig, gem) in table.items():
         if args.size and name != args.size:
             continue
         sizes[name] = {
             args.design: design_point(shape_of(**lig), lig["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
-            "gemma2": design_point(gemma_like(**gem), gem["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
-            "shapes": {args.design: lig, "gemma2": gem}}
+            beside: design_point(beside_shape(**gem), gem["vocab"], torch, rng, min(args.steps, 50), args.warmup, PROMPT, (1, 8, 64)),
+            "shapes": {args.design: lig, beside: gem}}
     print(json.dumps({"design": title, "dtype": "bf16",
                       "data": "synthetic: random weights, seeded uniform-random token ids", "prompt_len": PROMPT,
                       "sizes": sizes, "clocks": clocks.stop(), "peaks": peaks()}))
@@ -377,8 +415,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
     ap.add_argument("--context", type=int, default=PROMPT, help="prompt length of the --only decode case")
     ap.add_argument("--no-large", action="store_true", help="leave out the 9B and 27B shapes and the long contexts")
-    ap.add_argument("--design", choices=["ligirax", "dokulorn"], default=None,
-                    help="instead of the default workload: prefill and decode of this design beside Gemma 2 at equal layer sizes")
+    ap.add_argument("--design", choices=["ligirax", "dokulorn", "revepel"], default=None,
+                    help="instead of the default workload: prefill and decode of this design beside its closest registered design "
+                         "(Gemma 2; for revepel, Dokulorn) at equal layer sizes")
     ap.add_argument("--size", default=None, help="with --design: one of the sizes only")
     args = ap.parse_args()
 

@@ -107,7 +107,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // HD: head_dim padded to 64, 128 or 256 (head_dim itself is a multiple of 16).  EXACT: head_dim == HD;
 // row sizes and the swizzle are then compile-time constants and a fragment's address is a register
 // plus an immediate.
-template <int HD, bool EXACT>
+template <int HD, bool EXACT, bool SIG>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(AttentionArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long bar_storage[3];     // one per tile of the ring
@@ -271,6 +271,16 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // of heads 2 tq and 2 tq + 1
     const float LOG2E = 1.4426950408889634f;
+    // Sigmoid weights (no softmax): the weight of a key is sigmoid(score + bias[h]) by itself, so nothing is rescaled and
+    // nothing is divided in the end.  The merges below stay as they are: every maximum is 0 (all their weights are 1) and
+    // the normaliser is replaced by 1.  The weights reach the tensor cores as two bfloat16 terms (16 bits of them count).
+    constexpr bool sig = SIG;
+    float sb0 = 0.f, sb1 = 0.f;
+    if (sig) {
+        m0 = m1 = 0.f;
+        sb0 = (2 * tq < G ? a.sigmoid_bias[g * G + 2 * tq] : 0.f) * LOG2E;
+        sb1 = (2 * tq + 1 < G ? a.sigmoid_bias[g * G + 2 * tq + 1] : 0.f) * LOG2E;
+    }
     const bool capped = a.softcap > 0.f;
     const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
     const float c_out = a.softcap * LOG2E;
@@ -329,7 +339,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         const int w0 = warp * 16;                  // this warp's 16 keys of the page
         const bool active = w0 < r_end && w0 + 16 > r_begin;
         float c0 = 1.f, c1 = 1.f;
-        uint32_t pb0 = 0u, pb1 = 0u;
+        uint32_t pb0 = 0u, pb1 = 0u, pc0 = 0u, pc1 = 0u;
         if (active) {
             // ---- scores: rows = keys w0 + quad (+ 8), columns = heads 2 tq, 2 tq + 1 ----
             // four accumulators: the chain of dependent products is a quarter as long
@@ -354,6 +364,17 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
                 if (r < r_begin || r >= r_end) v = -INFINITY;
                 s[e] = v;
             }
+            if (sig) {
+                const float e0 = 1.0f / (1.0f + exp2f(-(s[0] + sb0))), e1 = 1.0f / (1.0f + exp2f(-(s[1] + sb1)));     // masked: exp2(inf) -> 0
+                const float e2 = 1.0f / (1.0f + exp2f(-(s[2] + sb0))), e3 = 1.0f / (1.0f + exp2f(-(s[3] + sb1)));
+                const uint32_t h01 = pack_bf16(e0, e1), h23 = pack_bf16(e2, e3);
+                const float2 f01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&h01));
+                const float2 f23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&h23));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(h01));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(h23));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pc0) : "r"(pack_bf16(e0 - f01.x, e1 - f01.y)));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pc1) : "r"(pack_bf16(e2 - f23.x, e3 - f23.y)));
+            } else {
             // maxima and sums over the 16 keys: over the two rows of a lane and over the lanes that differ in quad
             float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
@@ -378,6 +399,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             // P^T as the B operand: the [key][head] fragments transposed to [head][key]
             asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pack_bf16(e0, e1)));
             asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pack_bf16(e2, e3)));
+            }
         }
         __syncthreads();                                   // every warp is done with the key tile: its place takes tile ti + 3
         if (ti + 3 < n_tiles && tid == 0) issue(ti + 3);
@@ -407,6 +429,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
                     ldmatrix_x4_trans(af, v_addr(db));
                     o[db][0] *= c0; o[db][1] *= c1; o[db][2] *= c0; o[db][3] *= c1;
                     mma_bf16(o[db], af, pb0, pb1);
+                    if (sig) mma_bf16(o[db], af, pc0, pc1);
                 }
             }
         }
@@ -470,7 +493,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         }
         if (n_splits == 1) {
             if (a.sinks) lsum += exp2f(a.sinks[g * G + h] * LOG2E - M);    // a logit without key or value
-            const float inv = 1.0f / lsum;
+            const float inv = sig ? 1.0f : 1.0f / lsum;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
             o2[0] = __floats2bfloat162_rn(osum.x * inv, osum.y * inv);
             o2[1] = __floats2bfloat162_rn(osum.z * inv, osum.w * inv);
@@ -534,7 +557,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         }
         L = warp_sum(L);
         if (a.sinks) L += exp2f(a.sinks[g * G + h] * LOG2E - M);
-        if (lane == 0) inv_s[h] = 1.0f / L;
+        if (lane == 0) inv_s[h] = sig ? 1.0f : 1.0f / L;
     }
     __syncthreads();
     for (int idx = tid; idx < G * hd / 4; idx += DEC_THREADS) {
@@ -567,8 +590,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     }
 }
 
-template <int HD, bool EXACT>
-int launch_decode(const AttentionArgs* a, cudaStream_t st) {
+template <int HD, bool EXACT, bool SIG>
+int launch_decode_as(const AttentionArgs* a, cudaStream_t st) {
     const int tiles = 3 * a->page_size * a->head_dim * 2;
     const int merge = DEC_WARPS * QROWS * HD * (int)sizeof(float);
     const int runs = (QROWS * a->max_splits + QROWS) * (int)sizeof(float);
@@ -578,7 +601,7 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
                 a->page_size, a->head_dim, smem);
     static int granted = 32 * 1024;      // above this the kernel (which also has a few KB of static shared memory) opts in
     if (smem > granted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT, SIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "attention_decode");
         granted = smem;
     }
@@ -586,8 +609,14 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
     AttentionArgs b = *a;
     b.wait_cycles = rdl_wait_cycles_for(RDL_FAULT_ATTENTION_DECODE);
     b.test_extra_tx = rdl_test_extra_tx_for(RDL_FAULT_ATTENTION_DECODE);
-    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT>, grid, dim3(DEC_THREADS), (size_t)smem, st, b), "attention_decode");
+    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT, SIG>, grid, dim3(DEC_THREADS), (size_t)smem, st, b), "attention_decode");
     return 0;
+}
+
+// softmax, or sigmoid weights (a kernel of their own, so that the softmax kernels keep their registers)
+template <int HD, bool EXACT>
+int launch_decode(const AttentionArgs* a, cudaStream_t st) {
+    return a->sigmoid_bias ? launch_decode_as<HD, EXACT, true>(a, st) : launch_decode_as<HD, EXACT, false>(a, st);
 }
 
 }  // namespace

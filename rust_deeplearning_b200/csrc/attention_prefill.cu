@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
     return base + (uint32_t)((row * (HD / 8) + swizzled_chunk<HD>(row, chunk)) * 16);
 }
 
-template <int HD>
+template <int HD, bool SIG>
 __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionArgs a) {
     constexpr int CH = HD / 8;          // 16-byte chunks per row
     extern __shared__ __align__(128) unsigned char smem[];
@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
     for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const float LOG2E = 1.4426950408889634f;
+    constexpr bool sig = SIG;                                             // weights sigmoid(score + bias[h]), not normalised
+    const float sig_bias = sig ? a.sigmoid_bias[h] * LOG2E : 0.f;         // in the base-2 domain, like the scores
     const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
     const int ksteps = (hd + 15) / 16;
 
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
         // this warp's rows see nothing of the tile: skip its arithmetic (barriers stay outside)
         const bool warp_active = kv0 <= pw_last && (a.window == 0 || pw_first - (kv0 + BN - 1) < a.window);
         uint32_t pf[BN / 16][4];
+        uint32_t pl[BN / 16][4];      // sigmoid weights: what the rounding of pf left
         if (warp_active) {
             // ---- S = Q K^T ----
             float s[BN / 8][4];
@@ -182,6 +185,23 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            if (sig) {
+                // no softmax: the weight of a kept key is sigmoid(score + bias), formed in float and handed to the tensor
+                // cores as two bfloat16 terms (its rounding and what the rounding left), so that 16 bits of it count
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; ++nt) {
+                    float wv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) wv[e] = 1.0f / (1.0f + exp2f(-(s[nt][e] + sig_bias)));      // masked: exp2(inf) -> 0
+                    const uint32_t h01 = pack_bf16(wv[0], wv[1]), h23 = pack_bf16(wv[2], wv[3]);
+                    pf[nt >> 1][(nt & 1) * 2 + 0] = h01;
+                    pf[nt >> 1][(nt & 1) * 2 + 1] = h23;
+                    const float2 f01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&h01));
+                    const float2 f23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&h23));
+                    pl[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(wv[0] - f01.x, wv[1] - f01.y);
+                    pl[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(wv[2] - f23.x, wv[3] - f23.y);
+                }
+            } else {
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
             const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
             const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
@@ -206,6 +226,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
             for (int i = 0; i < HD / 8; ++i) {
                 o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
             }
+            }
         }
         __syncthreads();                       // every warp is done with the key tile
         if (has_next) issue(kv0 + BN, 0);      // the next keys travel while P V is computed
@@ -223,6 +244,10 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
                         ldmatrix_x4_trans(bf, tile_addr<HD>(sV, kk * 16 + (lane & 15), 2 * dp + (lane >> 4)));
                         mma_bf16(o[2 * dp], pf[kk], bf[0], bf[1]);
                         mma_bf16(o[2 * dp + 1], pf[kk], bf[2], bf[3]);
+                        if (sig) {
+                            mma_bf16(o[2 * dp], pl[kk], bf[0], bf[1]);
+                            mma_bf16(o[2 * dp + 1], pl[kk], bf[2], bf[3]);
+                        }
                     }
                 }
             }
@@ -238,7 +263,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
         l0 += exp2f(sink - m0);
         l1 += exp2f(sink - m1);
     }
-    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    const float i0 = sig ? 1.0f : 1.0f / l0, i1 = sig ? 1.0f : 1.0f / l1;
     __nv_bfloat16* out = (__nv_bfloat16*)a.out;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
@@ -254,18 +279,24 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
     }
 }
 
-template <int HD>
-int launch_prefill(const AttentionArgs* a, cudaStream_t st) {
+template <int HD, bool SIG>
+int launch_prefill_as(const AttentionArgs* a, cudaStream_t st) {
     const int smem = (BM + 2 * BN) * HD * 2;
     static bool opted = false;
     if (smem > 48 * 1024 && !opted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+        RDL_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<HD, SIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "attention_prefill");
         opted = true;
     }
     dim3 grid(a->n_tiles, a->n_heads);
-    RDL_CHECK_EX(rdl_launch(attention_prefill_kernel<HD>, grid, dim3(NTHREADS), (size_t)smem, st, *a), "attention_prefill");
+    RDL_CHECK_EX(rdl_launch(attention_prefill_kernel<HD, SIG>, grid, dim3(NTHREADS), (size_t)smem, st, *a), "attention_prefill");
     return 0;
+}
+
+// softmax, or sigmoid weights (a kernel of their own, so that the softmax kernels keep their registers)
+template <int HD>
+int launch_prefill(const AttentionArgs* a, cudaStream_t st) {
+    return a->sigmoid_bias ? launch_prefill_as<HD, true>(a, st) : launch_prefill_as<HD, false>(a, st);
 }
 
 }  // namespace

@@ -438,6 +438,7 @@ int launch_tc(dim3 grid, int smem, cudaStream_t st, const CUtensorMap& map_q, co
 extern "C" int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_width, void* stream) {
     if (int e = rdl_check_attention_args(a, "attention_prefill_tc")) return e;
     RDL_REQUIRE(a->dtype == RDL_BF16, "attention_prefill_tc: bfloat16 only");
+    RDL_REQUIRE(!a->sigmoid_bias, "attention_prefill_tc: sigmoid weights are the mma.sync prefill kernel's");
     RDL_REQUIRE(a->head_dim % 64 == 0 && a->head_dim <= 256, "attention_prefill_tc: head_dim %d must be 64, 128, 192 or 256", a->head_dim);
     RDL_REQUIRE(a->tile_seq && a->tile_q0 && a->n_tiles >= 0, "attention_prefill_tc: missing query tiles");
     RDL_REQUIRE(a->k_new && a->v_new && a->q_stride == row_width && a->kv_stride == row_width &&

@@ -189,8 +189,7 @@ class Attention:
             return self._forward_extended(x, batch, cache)
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
-        # sigmoid weights: the plain kernel, which forms every score and weight in float
-        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256 and self.score_bias is None
+        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
         fast_decode = fast and nh // nkv <= 8 and cache.page_size % 16 == 0 and cache.page_size <= 64
         common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale,
                       softcap=self.softcap, window=self.window, sigmoid_bias=self.score_bias)
@@ -256,7 +255,8 @@ class Attention:
             ab = batch.attention_batch("past", self.window)
             if fast and batch.n_tiles:
                 # prompts that start at position 0 read nothing from the cache: the tcgen05 kernel takes them
-                kind = "prefill_tc" if (hd % 64 == 0 and not batch.has_past) else "prefill"
+                # (sigmoid weights: the mma.sync kernel, which has them; the tcgen05 kernel's softmax runs a thread per row)
+                kind = "prefill_tc" if (hd % 64 == 0 and not batch.has_past and self.score_bias is None) else "prefill"
             else:
                 kind = "plain"
             ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width), kind=kind,

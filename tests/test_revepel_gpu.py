@@ -293,11 +293,14 @@ def _sigmoid_attention_ref(c, b, bias, new_kv, scale):
     return out
 
 
-@pytest.mark.parametrize("dtype,head_dim", [(torch.float32, 24), (torch.bfloat16, 40), (torch.bfloat16, 64)])
+@pytest.mark.parametrize("dtype,head_dim,fast", [(torch.float32, 24, False), (torch.bfloat16, 40, False), (torch.bfloat16, 64, False),
+                                                 (torch.bfloat16, 32, True), (torch.bfloat16, 64, True), (torch.bfloat16, 96, True),
+                                                 (torch.bfloat16, 128, True)])
 @pytest.mark.parametrize("window,decode", [(None, False), (None, True), (9, False), (9, True), (70, False), (70, True)])
-def test_attention_with_sigmoid_weights(dtype, head_dim, window, decode):
+def test_attention_with_sigmoid_weights(dtype, head_dim, fast, window, decode):
     """Weights sigmoid(score + bias per head), not normalised: against the key-by-key sum over cache pages in shuffled
-    order (a ring under a window) and the step's own rows, for prompts on a cached prefix and for single tokens."""
+    order (a ring under a window) and the step's own rows, for prompts on a cached prefix and for single tokens; the
+    plain kernel and the tensor-core kernels (prompts: mma.sync tiles; single tokens: split keys merged in the kernel)."""
     past = [130, 63, 67] if decode else [70, 0, 5]
     new = [1, 1, 1] if decode else [9, 140, 66]
     c = Case(past=past, new=new, n_heads=6, n_kv_heads=2, head_dim=head_dim, page_size=16, window=window, dtype=dtype, seed=61)
@@ -306,17 +309,23 @@ def test_attention_with_sigmoid_weights(dtype, head_dim, window, decode):
     if decode:
         ref.rope_cache(c.qkv, 6, 2, head_dim, tok_seq=c.tok_seq, tok_pos=c.tok_pos, pages=c.pages, seq_end=c.seq_end)
     extra = {} if decode else dict(new_kv=c.new_kv())
-    got = ops.attention(c.qkv, b, c.pages, kind="plain", sigmoid_bias=bias, **extra, **c.kw())
+    kind = "plain" if not fast else ("decode" if decode else "prefill")
+    if kind == "decode":
+        extra["keys_per_split"] = 32         # several runs of keys, merged by the last block
+    got = ops.attention(c.qkv, b, c.pages, kind=kind, sigmoid_bias=bias, **extra, **c.kw())
     want = _sigmoid_attention_ref(c, b, bias.cpu(), None if decode else c.new_kv(), c.kw()["score_scale"])
-    assert_close(got, want.to(dtype).to(DEV), dtype, rel=8.0, what="sigmoid weights")
+    assert_close(got, want.to(dtype).to(DEV), dtype, rel=8.0, what=f"sigmoid weights, {kind}")
+    if fast:      # two bfloat16 terms carry the weights: the tensor-core kernels stay close to the float kernel
+        plain_out = ops.attention(c.qkv, b, c.pages, kind="plain", sigmoid_bias=bias, **({} if decode else dict(new_kv=c.new_kv())), **c.kw())
+        assert_close(got, plain_out, dtype, rel=2.0, what=f"{kind} beside plain")
     with pytest.raises(Exception, match="sinks"):
         ops.attention(c.qkv, b, c.pages, kind="plain", sigmoid_bias=bias, sinks=bias, **extra, **c.kw())
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,fast", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("distance", [0, 1, 15, 16, 39, 40, 41, 200])
-def test_one_key_stands_out_inside_the_window_and_not_outside(dtype, decode, distance):
+def test_one_key_stands_out_inside_the_window_and_not_outside(dtype, fast, decode, distance):
     """A window of 40 on pages of 16: for the last query one key `distance` back is given a large score and every other
     weight is made tiny by the bias, so the output is that key's value while distance < 40 and next to nothing from 40
     on - in a prompt on a cached prefix, and for a single token over the ring."""
@@ -342,7 +351,8 @@ def test_one_key_stands_out_inside_the_window_and_not_outside(dtype, decode, dis
     bias = torch.tensor([-80.0, -80.0], dtype=torch.float32, device=DEV)     # the chosen key: 100 - 80; any other: below 50 - 80
     b = c.batch("all" if decode else "past")
     extra = {} if decode else dict(new_kv=c.new_kv())
-    got = ops.attention(c.qkv, b, c.pages, kind="plain", sigmoid_bias=bias, **extra, **c.kw(scale=1.0))[-1].float().cpu()
+    kind = "plain" if not fast else ("decode" if decode else "prefill")
+    got = ops.attention(c.qkv, b, c.pages, kind=kind, sigmoid_bias=bias, **extra, **c.kw(scale=1.0))[-1].float().cpu()
     for h in range(2):
         o = got[h * hd:(h + 1) * hd]
         if distance < W:
