@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 16
+#define RDL_ABI_VERSION 17
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -178,6 +178,11 @@ typedef struct {
     float* out;                                 // [tokens][heads * vdim]
 } RecurrenceArgs;
 int rdl_recurrence_scan(const RecurrenceArgs* a, void* stream);
+// The state space form in chunks of 64 tokens on tensor cores (csrc/state_space_chunked.cu): bfloat16 rows, state size and
+// head size multiples of 16 (state size up to 128), x, B and C on 16-byte boundaries; three launches; work: float scratch
+// of rdl_state_space_chunked_work_bytes bytes.
+int rdl_state_space_chunked(const RecurrenceArgs* a, void* work, long long work_bytes, void* stream);
+long long rdl_state_space_chunked_work_bytes(int n_tokens, int n_seqs, int n_heads, int dim, int vdim);
 typedef struct {
     int dtype, bias_dtype;
     int n_tokens, n_heads, n_key_heads, dim;

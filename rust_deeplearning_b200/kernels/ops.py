@@ -1259,13 +1259,21 @@ def _f32_vec(t, n, name):
     return t.data_ptr()
 
 
+def state_space_chunked_ok(rows: torch.Tensor, x_col: int, b_col: int, c_col: int, state_dim: int, vdim: int) -> bool:
+    """Whether the chunked kernels take these rows and sizes."""
+    return (rows.dtype is torch.bfloat16 and state_dim % 16 == 0 and 16 <= state_dim <= 128 and vdim % 16 == 0 and vdim >= 16
+            and rows.data_ptr() % 16 == 0 and rows.stride(0) % 8 == 0 and x_col % 8 == 0 and b_col % 8 == 0 and c_col % 8 == 0)
+
+
 def state_space_scan(rows: torch.Tensor, dt_rows: torch.Tensor, *, x_col: int, b_col: int, c_col: int, n_heads: int, n_groups: int,
                      state_dim: int, vdim: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: Optional[torch.Tensor],
-                     state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int) -> torch.Tensor:
-    """A selective state space, token by token, in float: per head h of group g,
+                     state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int, kind: str = "auto") -> torch.Tensor:
+    """A selective state space in float: per head h of group g,
     dt_t = softplus(dt_rows[t, h] + dt_bias[h]);  S_t = exp(-exp(a_log[h]) dt_t) S_(t-1) + dt_t B_t x_t^T;  y_t = S_t^T C_t + d_skip[h] x_t,
     with x [vdim] of head h from column x_col, B and C [state_dim] of group g from b_col and c_col of `rows`, S float32
-    [slots, heads, state_dim, vdim] read from and left in `state`.  Returns float32 [tokens, heads * vdim]."""
+    [slots, heads, state_dim, vdim] read from and left in `state`.  Returns float32 [tokens, heads * vdim].
+    kind: "scan" (token by token), "chunked" (bfloat16 rows, chunks of 64 tokens on tensor cores, three launches), "auto"
+    (chunks where sequences bring many tokens each)."""
     a = library.RecurrenceArgs()
     out = _recurrence_common(a, rows, state, n_heads, n_groups, state_dim, vdim, tok_pos, seq_start, slots, n_seqs)
     T = rows.shape[0]
@@ -1277,7 +1285,20 @@ def state_space_scan(rows: torch.Tensor, dt_rows: torch.Tensor, *, x_col: int, b
     a.dt_rows, a.dt_stride = dt_rows.data_ptr(), dt_rows.stride(0)
     a.dt_bias, a.a_log = _f32_vec(dt_bias, n_heads, "dt_bias"), _f32_vec(a_log, n_heads, "a_log")
     a.d_skip = _f32_vec(d_skip, n_heads, "d_skip") if d_skip is not None else None
-    library.check(library.load().rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
+    if kind == "auto":
+        many = T >= DECAY_CHUNKED_MIN_TOKENS and T >= DECAY_CHUNKED_MIN_PER_SEQUENCE * n_seqs
+        kind = "chunked" if (DECAY_CHUNKED and many and state_space_chunked_ok(rows, x_col, b_col, c_col, state_dim, vdim)) else "scan"
+    lib = library.load()
+    if kind == "scan":
+        library.check(lib.rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
+    elif kind == "chunked":
+        _need(state_space_chunked_ok(rows, x_col, b_col, c_col, state_dim, vdim),
+              "state_space_scan: the chunked kernels take bfloat16 rows, sizes in steps of 16 (state up to 128) and columns on 16-byte boundaries")
+        nbytes = lib.rdl_state_space_chunked_work_bytes(T, n_seqs, n_heads, state_dim, vdim)
+        work = torch.empty((nbytes // 4,), dtype=torch.float32, device=rows.device)
+        library.check(lib.rdl_state_space_chunked(ctypes.byref(a), _ptr(work), nbytes, _stream(rows)), 3)
+    else:
+        raise KernelError(f"state_space_scan: unknown kind '{kind}'")
     return out
 
 

@@ -166,10 +166,10 @@ def test_gated_sum_group_norm_with_the_gate_first_and_activations(dtype):
         assert_close(ops.linear(x, w, activation="relu2"), torch.from_numpy(want).to(dtype).to(DEV), dtype, what=f"relu2 after a product of {m} rows")
 
 
-def _ssm_case(H, G, N, P, lens, past, dtype, seed):
+def _ssm_case(H, G, N, P, lens, past, dtype, seed, lead=4):
     r = Rows(lens, past)
     inner = H * P
-    rows = rnd((r.T, inner + 2 * G * N + 4), dtype, seed, 0.8)[:, 4:]
+    rows = rnd((r.T, inner + 2 * G * N + lead), dtype, seed, 0.8)[:, lead:]
     dt_rows = rnd((r.T, H + 3), dtype, seed + 1)[:, 3:]
     dt_bias, a_log, d_skip = rnd((H,), torch.float32, seed + 2, 0.5), rnd((H,), torch.float32, seed + 3, 0.7), rnd((H,), torch.float32, seed + 4)
     a_log[0] = -9.0                                       # a head that forgets nothing
@@ -215,6 +215,27 @@ def test_state_space_scan(dtype, sizes):
             g1 = ops.state_space_scan(rows[t:t + 1], dt_rows[t:t + 1], state=st2, n_seqs=1, **o.where(), **kw)
             assert torch.equal(g1[0], got[t])
     assert torch.equal(st2, st)
+
+
+@pytest.mark.parametrize("sizes", [dict(H=4, G=2, N=16, P=16, lens=[130, 64, 1, 65], past=[0, 9, 3, 0]), dict(H=2, G=1, N=128, P=64, lens=[200], past=[0]),
+                                   dict(H=3, G=1, N=48, P=80, lens=[63, 129], past=[5, 0]), dict(H=2, G=2, N=32, P=144, lens=[2, 320], past=[0, 64])])
+def test_state_space_in_chunks(sizes):
+    """The chunked kernels against the plain recurrence and against the scan: chunks that end early, sequences of one and two
+    tokens beside long ones, carried states, a head that never decays, head sizes that need a second block of columns; and the
+    state they leave carries on, token by token, as the scan's does."""
+    r, rows, dt_rows, state, kw, want, want_state = _ssm_case(dtype=torch.bfloat16, seed=44, lead=8, **sizes)
+    assert ops.state_space_chunked_ok(rows, kw["x_col"], kw["b_col"], kw["c_col"], kw["state_dim"], kw["vdim"])
+    st, st_scan = state.clone(), state.clone()
+    got = ops.state_space_scan(rows, dt_rows, state=st, n_seqs=r.n, kind="chunked", **r.where(), **kw)
+    ref = ops.state_space_scan(rows, dt_rows, state=st_scan, n_seqs=r.n, kind="scan", **r.where(), **kw)
+    scale = max(1.0, float(np.abs(want).max()))
+    assert np.abs(_np(got) - want).max() <= 1e-4 * scale
+    assert np.abs(_np(got) - _np(ref)).max() <= 1e-4 * scale
+    assert np.abs(_np(st) - want_state).max() <= 1e-4 * max(1.0, float(np.abs(want_state).max()))
+    untouched = [i for i in range(r.n_slots) if i not in r.slot_ids.tolist()]
+    assert torch.equal(st[untouched], state[untouched])
+    with pytest.raises(ops.KernelError):
+        ops.state_space_scan(rows[:, 4:], dt_rows, state=st, n_seqs=r.n, kind="chunked", **r.where(), **{**kw, "b_col": kw["b_col"] - 4, "c_col": kw["c_col"] - 4})
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
