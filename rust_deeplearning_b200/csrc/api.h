@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 17
+#define RDL_ABI_VERSION 18
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -183,6 +183,10 @@ int rdl_recurrence_scan(const RecurrenceArgs* a, void* stream);
 // of rdl_state_space_chunked_work_bytes bytes.
 int rdl_state_space_chunked(const RecurrenceArgs* a, void* work, long long work_bytes, void* stream);
 long long rdl_state_space_chunked_work_bytes(int n_tokens, int n_seqs, int n_heads, int dim, int vdim);
+// The delta rule eight tokens at a time, in float (csrc/delta_rule_chunked.cu): heads of up to 128 key channels; two launches;
+// work: float scratch of rdl_delta_rule_chunked_work_bytes bytes, 16-byte aligned.
+int rdl_delta_rule_chunked(const RecurrenceArgs* a, void* work, long long work_bytes, void* stream);
+long long rdl_delta_rule_chunked_work_bytes(int n_tokens, int n_seqs, int n_heads, int dim, int vdim);
 typedef struct {
     int dtype, bias_dtype;
     int n_tokens, n_heads, n_key_heads, dim;

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -315,6 +315,7 @@ _SIGNATURES = {
     "rdl_recurrence_scan": [ctypes.POINTER(RecurrenceArgs), _P],
     "rdl_delta_prepare": [ctypes.POINTER(DeltaPrepareArgs), _P],
     "rdl_state_space_chunked": [ctypes.POINTER(RecurrenceArgs), _P, _LL, _P],
+    "rdl_delta_rule_chunked": [ctypes.POINTER(RecurrenceArgs), _P, _LL, _P],
     "rdl_decay_attention_scan": [ctypes.POINTER(DecayAttentionArgs), _P],
     "rdl_decay_attention_chunked": [ctypes.POINTER(DecayAttentionArgs), _P, _LL, _P],
     "rdl_decay_attention_chunks": [_I, _I],
@@ -372,6 +373,8 @@ def load():
         lib.rdl_attention_decode_scratch_bytes.restype = _LL
         lib.rdl_state_space_chunked_work_bytes.argtypes = [_I, _I, _I, _I, _I]
         lib.rdl_state_space_chunked_work_bytes.restype = _LL
+        lib.rdl_delta_rule_chunked_work_bytes.argtypes = [_I, _I, _I, _I, _I]
+        lib.rdl_delta_rule_chunked_work_bytes.restype = _LL
         lib.rdl_latent_decode_scratch_bytes.argtypes = [_I, _I, _I, _I]
         lib.rdl_latent_decode_scratch_bytes.restype = _LL
         lib.rdl_sampling_uniform.argtypes = [ctypes.c_ulonglong] * 3

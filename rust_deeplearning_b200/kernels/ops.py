@@ -1302,6 +1302,9 @@ def state_space_scan(rows: torch.Tensor, dt_rows: torch.Tensor, *, x_col: int, b
     return out
 
 
+DELTA_CHUNKED_MAX_DIM = 128
+
+
 def delta_prepare(rows: torch.Tensor, *, q_col: int, k_col: int, n_heads: int, n_key_heads: int, dim: int, decay_rows: torch.Tensor,
                   beta_rows: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, q_scale: float, unit_eps: float):
     """What enters a delta-rule recurrence, in float32: q and k of every key head as unit vectors, v / sqrt(sum(v^2) + unit_eps)
@@ -1330,11 +1333,14 @@ def delta_prepare(rows: torch.Tensor, *, q_col: int, k_col: int, n_heads: int, n
 
 
 def delta_rule_scan(rows: torch.Tensor, *, v_col: int, q_f, k_f, g_f, beta_f, n_heads: int, n_key_heads: int, dim: int, vdim: int,
-                    state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int) -> torch.Tensor:
-    """The delta rule with a decay per key channel, token by token, in float: per head h with key head j(h),
+                    state: torch.Tensor, tok_pos, seq_start, slots, n_seqs: int, kind: str = "auto") -> torch.Tensor:
+    """The delta rule with a decay per key channel, in float: per head h with key head j(h),
     S <- g_t (.) S (row i times g_t[i]);  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t,
     v [vdim] of head h from column v_col of `rows`, the rest as `delta_prepare` made it; S float32 [slots, heads, dim, vdim]
-    read from and left in `state`.  Returns float32 [tokens, heads * vdim]."""
+    read from and left in `state`.  Returns float32 [tokens, heads * vdim].
+    kind: "scan" (token by token), "chunked" (eight tokens at a time: what depends on no state is made for all groups at
+    once, the state takes a group's writes in one pass; heads of up to 128 key channels), "auto" (groups where sequences
+    bring many bfloat16 tokens each)."""
     a = library.RecurrenceArgs()
     out = _recurrence_common(a, rows, state, n_heads, n_key_heads, dim, vdim, tok_pos, seq_start, slots, n_seqs)
     T = rows.shape[0]
@@ -1343,5 +1349,18 @@ def delta_rule_scan(rows: torch.Tensor, *, v_col: int, q_f, k_f, g_f, beta_f, n_
         _need(t.dtype is torch.float32 and t.is_contiguous() and tuple(t.shape) == (T, n), f"delta_rule_scan: {name} must be float32 [{T}, {n}]")
     a.mode, a.v_col = library.REC_DELTA, v_col
     a.q_f, a.k_f, a.g_f, a.beta_f = q_f.data_ptr(), k_f.data_ptr(), g_f.data_ptr(), beta_f.data_ptr()
-    library.check(library.load().rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
+    if kind == "auto":
+        many = T >= DECAY_CHUNKED_MIN_TOKENS and T >= DECAY_CHUNKED_MIN_PER_SEQUENCE * n_seqs
+        # float32 rows stay token by token: there a step's cut leaves the same bits
+        kind = "chunked" if (DECAY_CHUNKED and many and rows.dtype is torch.bfloat16 and dim <= DELTA_CHUNKED_MAX_DIM) else "scan"
+    lib = library.load()
+    if kind == "scan":
+        library.check(lib.rdl_recurrence_scan(ctypes.byref(a), _stream(rows)))
+    elif kind == "chunked":
+        _need(dim <= DELTA_CHUNKED_MAX_DIM, f"delta_rule_scan: the chunked kernels take heads of up to {DELTA_CHUNKED_MAX_DIM} key channels")
+        nbytes = lib.rdl_delta_rule_chunked_work_bytes(T, n_seqs, n_heads, dim, vdim)
+        work = torch.empty((nbytes // 4,), dtype=torch.float32, device=rows.device)
+        library.check(lib.rdl_delta_rule_chunked(ctypes.byref(a), _ptr(work), nbytes, _stream(rows)), 2)
+    else:
+        raise KernelError(f"delta_rule_scan: unknown kind '{kind}'")
     return out

@@ -240,8 +240,12 @@ def test_state_space_in_chunks(sizes):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [dict(H=4, J=2, d=16, e=24, lens=[33, 1, 2], past=[0, 7, 0]), dict(H=3, J=1, d=12, e=20, lens=[5, 70], past=[3, 0]),
-                                   dict(H=2, J=2, d=64, e=64, lens=[40], past=[0]), dict(H=1, J=1, d=130, e=33, lens=[6, 1], past=[2, 0])])
+                                   dict(H=2, J=2, d=64, e=64, lens=[40], past=[0]), dict(H=1, J=1, d=130, e=33, lens=[6, 1], past=[2, 0]),
+                                   dict(H=2, J=1, d=128, e=48, lens=[17, 8, 1, 9], past=[0, 4, 2, 0]), dict(H=2, J=2, d=72, e=16, lens=[64, 7], past=[0, 0])])
 def test_delta_rule_preparation_and_scan(dtype, sizes):
+    """The prepared vectors and both forms of the recurrence against the plain one from a carried state: token by token
+    (one token a step gives the same bits), and eight tokens at a time (groups that end early, sequences of one token
+    beside long ones, head sizes that are no multiples of anything)."""
     H, J, d, e, lens, past = (sizes[k] for k in ("H", "J", "d", "e", "lens", "past"))
     r = Rows(lens, past)
     rows = rnd((r.T, 2 * J * d + H * e + 4), dtype, 50, 0.8)[:, 4:]
@@ -277,15 +281,25 @@ def test_delta_rule_preparation_and_scan(dtype, sizes):
             want_state[int(r.slot_ids[s]), h] = S
     kw = dict(v_col=2 * J * d, n_heads=H, n_key_heads=J, dim=d, vdim=e)
     st = state.clone()
-    got = ops.delta_rule_scan(rows, q_f=q_f, k_f=k_f, g_f=g_f, beta_f=beta_f, state=st, n_seqs=r.n, **r.where(), **kw)
+    got = ops.delta_rule_scan(rows, q_f=q_f, k_f=k_f, g_f=g_f, beta_f=beta_f, state=st, n_seqs=r.n, kind="scan", **r.where(), **kw)
     assert np.abs(_np(got) - want).max() <= 3e-5 * max(1.0, float(np.abs(want).max()))
     assert np.abs(_np(st) - want_state).max() <= 3e-5 * max(1.0, float(np.abs(want_state).max()))
+    untouched = [i for i in range(r.n_slots) if i not in r.slot_ids.tolist()]
+    if d <= ops.DELTA_CHUNKED_MAX_DIM:
+        st3 = state.clone()
+        got3 = ops.delta_rule_scan(rows, q_f=q_f, k_f=k_f, g_f=g_f, beta_f=beta_f, state=st3, n_seqs=r.n, kind="chunked", **r.where(), **kw)
+        assert np.abs(_np(got3) - want).max() <= 3e-5 * max(1.0, float(np.abs(want).max()))
+        assert np.abs(_np(st3) - want_state).max() <= 3e-5 * max(1.0, float(np.abs(want_state).max()))
+        assert torch.equal(st3[untouched], state[untouched])
+    else:
+        with pytest.raises(ops.KernelError):
+            ops.delta_rule_scan(rows, q_f=q_f, k_f=k_f, g_f=g_f, beta_f=beta_f, state=state.clone(), n_seqs=r.n, kind="chunked", **r.where(), **kw)
     st2 = state.clone()
     for s in range(r.n):
         for t in range(r.starts[s], r.starts[s + 1]):
             o = r.one(s, t)
             sl = slice(t, t + 1)
-            g1 = ops.delta_rule_scan(rows[sl], q_f=q_f[sl], k_f=k_f[sl], g_f=g_f[sl], beta_f=beta_f[sl], state=st2, n_seqs=1, **o.where(), **kw)
+            g1 = ops.delta_rule_scan(rows[sl], q_f=q_f[sl], k_f=k_f[sl], g_f=g_f[sl], beta_f=beta_f[sl], state=st2, n_seqs=1, kind="scan", **o.where(), **kw)
             assert torch.equal(g1[0], got[t])
     assert torch.equal(st2, st)
 
