@@ -192,7 +192,9 @@ class Attention:
         fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
         fast_decode = fast and nh // nkv <= 8 and cache.page_size % 16 == 0 and cache.page_size <= 64
         common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale,
-                      softcap=self.softcap, window=self.window, sigmoid_bias=self.score_bias)
+                      softcap=self.softcap, window=self.window)
+        if self.score_bias is not None:
+            common["sigmoid_bias"] = self.score_bias
         tables, rotary_dim = self._rotary_tables()
         if cache.owns_kv and not self.has_kv:
             raise ValueError("attention: a run without key and value projections must read another run's cache")
