@@ -211,10 +211,33 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(RecurrenceArgs a
     src.has_v = v_wide && lane < (int)(DR_COLS * sizeof(T) / 16);
     src.beta = a.beta_f + (long long)row0 * a.n_heads + h;
     src.beta_step = a.n_heads;
+    // The block's eight columns of the state come through shared memory: two lanes fetch a row's 32 bytes side by side, so
+    // that a step of single tokens, which is nothing but this fetch and its store, moves whole sectors.
+    float* tile = dr_ring + DR_STAGES * L::FLOATS;          // [16 RPS rows][9]
+    float* Sb = a.state + (((long long)a.slots[seq] * a.n_heads + h) * dim) * vdim + c0;
+    const bool s_wide = (vdim & 3) == 0 && c0 + DR_COLS <= vdim && ((uintptr_t)a.state & 15) == 0;
+    for (int idx = tid; idx < 32 * RPS; idx += DR_THREADS) {
+        const int row = idx >> 1, c4 = 4 * (idx & 1);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < dim) {
+            const float* from = Sb + (long long)row * vdim + c4;
+            if (s_wide) v = *reinterpret_cast<const float4*>(from);
+            else {
+                if (c0 + c4 < vdim) v.x = from[0];
+                if (c0 + c4 + 1 < vdim) v.y = from[1];
+                if (c0 + c4 + 2 < vdim) v.z = from[2];
+                if (c0 + c4 + 3 < vdim) v.w = from[3];
+            }
+        }
+        float* to = tile + row * 9 + c4;
+        to[0] = v.x; to[1] = v.y; to[2] = v.z; to[3] = v.w;
+    }
     // rows beyond the head's last: q = k = 0 and g = 1 in every stage, never written again
-    for (int i = tid; i < DR_STAGES * L::FLOATS; i += DR_THREADS) {
-        const int w = i % L::FLOATS;
-        dr_ring[i] = (w >= 2 * L::VEC && w < 3 * L::VEC) ? 1.f : 0.f;
+    if (dim < 16 * RPS) {
+        for (int i = tid; i < DR_STAGES * L::FLOATS; i += DR_THREADS) {
+            const int w = i % L::FLOATS;
+            dr_ring[i] = (w >= 2 * L::VEC && w < 3 * L::VEC) ? 1.f : 0.f;
+        }
     }
     __syncthreads();
 #pragma unroll
@@ -222,10 +245,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(RecurrenceArgs a
         if (d < n) dr_ask<T, RPS>(a, src, d, dr_ring + d * L::FLOATS, warp, lane, row0 + d, h, kh, wide);
         dr_commit();
     }
-    float* S = a.state + (((long long)a.slots[seq] * a.n_heads + h) * dim) * vdim + col;
     float s[RPS];
 #pragma unroll
-    for (int i = 0; i < RPS; ++i) s[i] = (col_ok && r * RPS + i < dim) ? S[(long long)(r * RPS + i) * vdim] : 0.f;
+    for (int i = 0; i < RPS; ++i) s[i] = tile[(r * RPS + i) * 9 + bc];
     float* out = a.out + (long long)row0 * a.n_heads * vdim + (long long)h * vdim + col;
     const int out_step = a.n_heads * vdim;
 
@@ -276,14 +298,27 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(RecurrenceArgs a
     }
     dr_wait_all();
 #pragma unroll
-    for (int i = 0; i < RPS; ++i)
-        if (col_ok && r * RPS + i < dim) S[(long long)(r * RPS + i) * vdim] = s[i];
+    for (int i = 0; i < RPS; ++i) tile[(r * RPS + i) * 9 + bc] = s[i];
+    __syncthreads();
+    for (int idx = tid; idx < 32 * RPS; idx += DR_THREADS) {
+        const int row = idx >> 1, c4 = 4 * (idx & 1);
+        if (row >= dim) continue;
+        const float* from = tile + row * 9 + c4;
+        float* to = Sb + (long long)row * vdim + c4;
+        if (s_wide) *reinterpret_cast<float4*>(to) = make_float4(from[0], from[1], from[2], from[3]);
+        else {
+            if (c0 + c4 < vdim) to[0] = from[0];
+            if (c0 + c4 + 1 < vdim) to[1] = from[1];
+            if (c0 + c4 + 2 < vdim) to[2] = from[2];
+            if (c0 + c4 + 3 < vdim) to[3] = from[3];
+        }
+    }
 }
 
 template <typename T, int RPS>
 cudaError_t launch_delta_rule_rows(const RecurrenceArgs* a, cudaStream_t st) {
     const dim3 grid(a->n_seqs, a->n_heads, (a->vdim + DR_COLS - 1) / DR_COLS);
-    return rdl_launch(delta_rule_kernel<T, RPS>, grid, dim3(DR_THREADS), (size_t)DR_STAGES * DrStage<RPS>::FLOATS * sizeof(float), st, *a);
+    return rdl_launch(delta_rule_kernel<T, RPS>, grid, dim3(DR_THREADS), (size_t)(DR_STAGES * DrStage<RPS>::FLOATS + 16 * RPS * 9) * sizeof(float), st, *a);
 }
 
 template <typename T>

@@ -36,8 +36,12 @@ __global__ void __launch_bounds__(256) norm_shift_kernel(const float* __restrict
     rdl_grid_launch_dependents();
     const int t = blockIdx.x;
     const float* xr = x + (long long)t * width;
-    const float inv = 1.0f / sqrtf(row_square_sum(xr, width, scratch) / (float)width + eps);
+    // the batch description first: its dependent loads travel while the row is summed
     const int p = tok_pos[t];
+    const int seq = p < 0 ? 0 : tok_seq[t];
+    const int row0 = seq_start[seq], last = seq_start[seq + 1] - 1;
+    float* st = state + (long long)slots[seq] * width;
+    const float inv = 1.0f / sqrtf(row_square_sum(xr, width, scratch) / (float)width + eps);
     if (p < 0) {   // a padding row of a fixed-size batch: finite values, no slot
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             const T v = from_float<T>(xr[i] * inv * rdl_load(w, i, w_dtype));
@@ -46,25 +50,41 @@ __global__ void __launch_bounds__(256) norm_shift_kernel(const float* __restrict
         }
         return;
     }
-    const int seq = tok_seq[t], row0 = seq_start[seq];
     const bool first = t == row0;
     float inv_prev = 0.f;
     const float* xp = xr - width;
     if (!first) inv_prev = 1.0f / sqrtf(row_square_sum(xp, width, scratch) / (float)width + eps);
-    float* st = state + (long long)slots[seq] * width;
-    const int last = seq_start[seq + 1] - 1;
     float inv_last = inv;
     const float* xl = x + (long long)last * width;
     if (first && last != t) inv_last = 1.0f / sqrtf(row_square_sum(xl, width, scratch) / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float wi = rdl_load(w, i, w_dtype);
-        const float n = xr[i] * inv * wi;
-        float prev;
-        if (!first) prev = xp[i] * inv_prev * wi;
-        else prev = p == 0 ? 0.f : st[i];
-        normed[(long long)t * width + i] = from_float<T>(n);
-        mixed[(long long)t * width + i] = from_float<T>(n + (prev - n) * rdl_load(shift, i, shift_dtype));
-        if (first) st[i] = xl[i] * inv_last * wi;
+    // four elements a thread at a time, every load before the first store: the loads of a row are one trip to memory
+    for (int i0 = threadIdx.x; i0 < width; i0 += 4 * blockDim.x) {
+        float xv[4], wv[4], sv[4], pv[4], lv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x;
+            xv[u] = wv[u] = sv[u] = pv[u] = lv[u] = 0.f;
+            if (i < width) {
+                xv[u] = xr[i];
+                wv[u] = rdl_load(w, i, w_dtype);
+                sv[u] = rdl_load(shift, i, shift_dtype);
+                if (!first) pv[u] = xp[i];
+                else {
+                    pv[u] = p == 0 ? 0.f : st[i];
+                    lv[u] = xl[i];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i >= width) continue;
+            const float n = xv[u] * inv * wv[u];
+            const float prev = first ? pv[u] : pv[u] * inv_prev * wv[u];
+            normed[(long long)t * width + i] = from_float<T>(n);
+            mixed[(long long)t * width + i] = from_float<T>(n + (prev - n) * sv[u]);
+            if (first) st[i] = lv[u] * inv_last * wv[u];
+        }
     }
 }
 
@@ -143,6 +163,50 @@ __global__ void gated_residual_kernel(float* __restrict__ res, const T* __restri
     }
 }
 
+// the same sum for bfloat16 rows whose width is a multiple of 8: eight elements a thread, 16-byte accesses, one division
+// by the width a thread instead of a 64-bit one an element; every element goes through the same operations as above
+__global__ void __launch_bounds__(256) gated_residual_vec_kernel(float* __restrict__ res, const __nv_bfloat16* __restrict__ gates, long long gates_stride,
+                                                                 const void* __restrict__ bias_a, const void* __restrict__ bias_b, int bias_dtype,
+                                                                 const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b1,
+                                                                 const __nv_bfloat16* __restrict__ b2, int width, int groups) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int per_row = width >> 3;
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < groups; v += gridDim.x * blockDim.x) {
+        const int t = v / per_row, i = (v - t * per_row) << 3;
+        const long long idx = (long long)t * width + i;
+        const uint4 ga4 = *reinterpret_cast<const uint4*>(gates + t * gates_stride + i);
+        const uint4 a4 = *reinterpret_cast<const uint4*>(a + idx);
+        uint4 gb4 = make_uint4(0, 0, 0, 0), b14 = gb4, b24 = gb4;
+        if (b1) {
+            gb4 = *reinterpret_cast<const uint4*>(gates + t * gates_stride + width + i);
+            b14 = *reinterpret_cast<const uint4*>(b1 + idx);
+            if (b2) b24 = *reinterpret_cast<const uint4*>(b2 + idx);
+        }
+        float4 r0 = *reinterpret_cast<const float4*>(res + idx), r1 = *reinterpret_cast<const float4*>(res + idx + 4);
+        const __nv_bfloat16* gav = reinterpret_cast<const __nv_bfloat16*>(&ga4);
+        const __nv_bfloat16* gbv = reinterpret_cast<const __nv_bfloat16*>(&gb4);
+        const __nv_bfloat16* av = reinterpret_cast<const __nv_bfloat16*>(&a4);
+        const __nv_bfloat16* b1v = reinterpret_cast<const __nv_bfloat16*>(&b14);
+        const __nv_bfloat16* b2v = reinterpret_cast<const __nv_bfloat16*>(&b24);
+        float o[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float ga = __bfloat162float(gav[e]) + rdl_load(bias_a, i + e, bias_dtype);
+            float sum = __bfloat162float(av[e]) / (1.0f + expf(-ga));
+            if (b1) {
+                const float gb = __bfloat162float(gbv[e]) + rdl_load(bias_b, i + e, bias_dtype);
+                float f = __bfloat162float(b1v[e]);
+                if (b2) f += __bfloat162float(b2v[e]);
+                sum += f / (1.0f + expf(-gb));
+            }
+            o[e] += sum;
+        }
+        *reinterpret_cast<float4*>(res + idx) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(res + idx + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, long long total, int act) {
     rdl_grid_wait();
@@ -210,7 +274,13 @@ extern "C" int rdl_gated_residual_add(float* res, const void* gates, long long g
     const long long total = (long long)n_rows * width;
     const dim3 grid((unsigned)min((total + 255) / 256, 65535LL * 16)), block(256);
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == RDL_BF16)
+    const bool aligned = (((uintptr_t)res | (uintptr_t)gates | (uintptr_t)a | (uintptr_t)b1 | (uintptr_t)b2) & 15) == 0;
+    if (dtype == RDL_BF16 && width % 8 == 0 && gates_stride % 8 == 0 && aligned && total / 8 < (1LL << 31)) {
+        const int groups = (int)(total / 8);
+        RDL_CHECK_EX(rdl_launch(gated_residual_vec_kernel, dim3((unsigned)min((groups + 255) / 256, 148 * 16)), block, 0, st, res, (const __nv_bfloat16*)gates,
+                                gates_stride, bias_a, bias_b, bias_dtype, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b1, (const __nv_bfloat16*)b2, width, groups),
+                     "gated_residual_add");
+    } else if (dtype == RDL_BF16)
         RDL_CHECK_EX(rdl_launch(gated_residual_kernel<__nv_bfloat16>, grid, block, 0, st, res, (const __nv_bfloat16*)gates, gates_stride, bias_a, bias_b,
                                 bias_dtype, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b1, (const __nv_bfloat16*)b2, width, total),
                      "gated_residual_add");
