@@ -36,12 +36,8 @@ __global__ void __launch_bounds__(256) norm_shift_kernel(const float* __restrict
     rdl_grid_launch_dependents();
     const int t = blockIdx.x;
     const float* xr = x + (long long)t * width;
-    // the batch description first: its dependent loads travel while the row is summed
-    const int p = tok_pos[t];
-    const int seq = p < 0 ? 0 : tok_seq[t];
-    const int row0 = seq_start[seq], last = seq_start[seq + 1] - 1;
-    float* st = state + (long long)slots[seq] * width;
     const float inv = 1.0f / sqrtf(row_square_sum(xr, width, scratch) / (float)width + eps);
+    const int p = tok_pos[t];
     if (p < 0) {   // a padding row of a fixed-size batch: finite values, no slot
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             const T v = from_float<T>(xr[i] * inv * rdl_load(w, i, w_dtype));
@@ -50,41 +46,25 @@ __global__ void __launch_bounds__(256) norm_shift_kernel(const float* __restrict
         }
         return;
     }
+    const int seq = tok_seq[t], row0 = seq_start[seq];
     const bool first = t == row0;
     float inv_prev = 0.f;
     const float* xp = xr - width;
     if (!first) inv_prev = 1.0f / sqrtf(row_square_sum(xp, width, scratch) / (float)width + eps);
+    float* st = state + (long long)slots[seq] * width;
+    const int last = seq_start[seq + 1] - 1;
     float inv_last = inv;
     const float* xl = x + (long long)last * width;
     if (first && last != t) inv_last = 1.0f / sqrtf(row_square_sum(xl, width, scratch) / (float)width + eps);
-    // four elements a thread at a time, every load before the first store: the loads of a row are one trip to memory
-    for (int i0 = threadIdx.x; i0 < width; i0 += 4 * blockDim.x) {
-        float xv[4], wv[4], sv[4], pv[4], lv[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * blockDim.x;
-            xv[u] = wv[u] = sv[u] = pv[u] = lv[u] = 0.f;
-            if (i < width) {
-                xv[u] = xr[i];
-                wv[u] = rdl_load(w, i, w_dtype);
-                sv[u] = rdl_load(shift, i, shift_dtype);
-                if (!first) pv[u] = xp[i];
-                else {
-                    pv[u] = p == 0 ? 0.f : st[i];
-                    lv[u] = xl[i];
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * blockDim.x;
-            if (i >= width) continue;
-            const float n = xv[u] * inv * wv[u];
-            const float prev = first ? pv[u] : pv[u] * inv_prev * wv[u];
-            normed[(long long)t * width + i] = from_float<T>(n);
-            mixed[(long long)t * width + i] = from_float<T>(n + (prev - n) * sv[u]);
-            if (first) st[i] = lv[u] * inv_last * wv[u];
-        }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float wi = rdl_load(w, i, w_dtype);
+        const float n = xr[i] * inv * wi;
+        float prev;
+        if (!first) prev = xp[i] * inv_prev * wi;
+        else prev = p == 0 ? 0.f : st[i];
+        normed[(long long)t * width + i] = from_float<T>(n);
+        mixed[(long long)t * width + i] = from_float<T>(n + (prev - n) * rdl_load(shift, i, shift_dtype));
+        if (first) st[i] = xl[i] * inv_last * wi;
     }
 }
 
