@@ -13,7 +13,8 @@
 // out as the second launch reads it), together with beta and v in float.  The second launch walks each sequence's groups:
 // a block of eight warps per 16 columns of a head's state, lane (column, slice) with RPS rows of its column in registers.
 // For a group a lane forms its parts of the 16 sums S^T kd_t and S^T qd_t in one pass, the sixteen lanes of a column add
-// them in one round of exchanges, every lane solves the small triangular system for u_1..u_C by substitution, and the
+// them in one round of exchanges, u = T r and o = S^T qd + (B T) r follow as one row of products a lane (the triangular
+// system's inverse T = (I + diag(beta) A)^-1 diag(beta) and B T depend on no state and come with the record), and the
 // state takes all eight writes in one pass: two dependent passes and one round of exchanges per eight tokens instead of
 // per token.  The records of the next groups are on their way into shared memory (asynchronous copies) meanwhile.
 #include "api.h"
@@ -30,7 +31,7 @@ constexpr int DC_SCALARS = 2 * DC_C * DC_C + DC_C;      // A, B, beta
 
 // A record in floats: 3 C + 1 vectors (kd_t, qd_t, w_t for every t, then P(0, C)), each as sixteen slices of RPS rows (a
 // slice starts 16 bytes after the one before it would end where that keeps eight slices' 16-byte reads in different banks);
-// then A [C][C], B [C][C], beta [C]; then v [C][columns rounded up to 16].
+// then T [C][C], B T [C][C], beta [C]; then v [C][columns rounded up to 16].
 template <int RPS> struct DcRecord {
     static constexpr int SLICE = RPS == 4 ? 4 : RPS + 4, VEC = 16 * SLICE, SC = (3 * DC_C + 1) * VEC, V = SC + DC_SCALARS;
     static constexpr int STAGE = V + DC_C * DC_COLS;          // what a block keeps of a record
@@ -116,12 +117,40 @@ __global__ void __launch_bounds__(128) dc_record_kernel(RecurrenceArgs a, float*
         if (lane == 0) part[warp][i] = s;
     }
     __syncthreads();
+    __shared__ float fin[2 * DC_C * DC_C], tm[DC_C * DC_C], bet[DC_C];
     for (int i = tid; i < 2 * DC_C * DC_C; i += 128) {
         const int t = (i % (DC_C * DC_C)) / DC_C, j = i % DC_C;
         const bool used = j < t || (j == t && i >= DC_C * DC_C);
-        rec[R::SC + i] = used ? ((part[0][i] + part[1][i]) + (part[2][i] + part[3][i])) : 0.f;
+        fin[i] = used ? ((part[0][i] + part[1][i]) + (part[2][i] + part[3][i])) : 0.f;
     }
-    if (tid < DC_C) rec[R::SC + 2 * DC_C * DC_C + tid] = tid < L ? a.beta_f[(long long)(row0 + tid) * a.n_heads + h] : 0.f;
+    if (tid < DC_C) bet[tid] = tid < L ? a.beta_f[(long long)(row0 + tid) * a.n_heads + h] : 0.f;
+    __syncthreads();
+    // u = T r with r_t = v_t - S^T kd_t and T = (I + diag(beta) A)^-1 diag(beta): thread j forms column j by substitution
+    if (tid < DC_C) {
+        const int j = tid;
+        float x[DC_C];
+#pragma unroll
+        for (int t = 0; t < DC_C; ++t) x[t] = t == j ? 1.f : 0.f;
+#pragma unroll
+        for (int t = 1; t < DC_C; ++t) {
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < t; ++i) acc = fmaf(fin[t * DC_C + i], x[i], acc);
+            if (t > j) x[t] = -bet[t] * acc;
+        }
+#pragma unroll
+        for (int t = 0; t < DC_C; ++t) tm[t * DC_C + j] = x[t] * bet[j];
+    }
+    __syncthreads();
+    // o = S^T qd + (B T) r
+    if (tid < DC_C * DC_C) {
+        const int t = tid / DC_C, j = tid % DC_C;
+        float acc = 0.f;
+        for (int i = j; i <= t; ++i) acc = fmaf(fin[DC_C * DC_C + t * DC_C + i], tm[i * DC_C + j], acc);
+        rec[R::SC + tid] = tm[tid];
+        rec[R::SC + DC_C * DC_C + tid] = acc;
+    }
+    if (tid < DC_C) rec[R::SC + 2 * DC_C * DC_C + tid] = bet[tid];
     const int vp = (vdim + DC_COLS - 1) / DC_COLS * DC_COLS;
     const T* rows = (const T*)a.rows;
     for (int i = tid; i < DC_C * vp; i += 128) {
@@ -233,26 +262,23 @@ __global__ void __launch_bounds__(DC_THREADS) dc_scan_kernel(RecurrenceArgs a, c
         }
         const float z = dc_sum16(x, r);
         const float* sc = stage + R::SC;
-        // u_t by substitution, o_t beside it; every lane of the column does the same
-        float u[DC_C];
+        // Lanes 0..7 of a column hold S^T kd_t, lanes 8..15 S^T qd_t.  r_t = v_t - S^T kd_t goes to every lane; lane t then
+        // forms u_t = (T r)_t and lane 8 + t o_t = S^T qd_t + (B T r)_t, a row of eight products each.
         const int left = n - gi * DC_C;
+        const int tt = r & 7;
+        const float val = r < DC_C ? stage[R::V + tt * DC_COLS + bc] - z : z;
+        float rj[DC_C];
 #pragma unroll
-        for (int t = 0; t < DC_C; ++t) {
-            const float sk = __shfl_sync(full, z, t, 16), sq = __shfl_sync(full, z, DC_C + t, 16);
-            const float4 a_lo = *reinterpret_cast<const float4*>(sc + t * DC_C), a_hi = *reinterpret_cast<const float4*>(sc + t * DC_C + 4);
-            const float4 b_lo = *reinterpret_cast<const float4*>(sc + DC_C * DC_C + t * DC_C), b_hi = *reinterpret_cast<const float4*>(sc + DC_C * DC_C + t * DC_C + 4);
-            const float ar[DC_C] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-            const float br[DC_C] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
-            float rest = stage[R::V + t * DC_COLS + bc] - sk, o = sq;
+        for (int j = 0; j < DC_C; ++j) rj[j] = __shfl_sync(full, val, j, 16);
+        const float* mrow = sc + r * DC_C;            // row t of T for lanes 0..7, row t of B T for lanes 8..15
+        const float4 m_lo = *reinterpret_cast<const float4*>(mrow), m_hi = *reinterpret_cast<const float4*>(mrow + 4);
+        float acc = r < DC_C ? 0.f : z;
+        acc = fmaf(m_lo.x, rj[0], acc); acc = fmaf(m_lo.y, rj[1], acc); acc = fmaf(m_lo.z, rj[2], acc); acc = fmaf(m_lo.w, rj[3], acc);
+        acc = fmaf(m_hi.x, rj[4], acc); acc = fmaf(m_hi.y, rj[5], acc); acc = fmaf(m_hi.z, rj[6], acc); acc = fmaf(m_hi.w, rj[7], acc);
+        if (r >= DC_C && col_ok && tt < left) out[(long long)(gi * DC_C + tt) * out_step] = acc;
+        float u[DC_C];
 #pragma unroll
-            for (int j = 0; j < t; ++j) {
-                rest = fmaf(-ar[j], u[j], rest);
-                o = fmaf(br[j], u[j], o);
-            }
-            u[t] = sc[2 * DC_C * DC_C + t] * rest;
-            o = fmaf(br[t], u[t], o);
-            if (r == 0 && col_ok && t < left) out[(long long)(gi * DC_C + t) * out_step] = o;
-        }
+        for (int j = 0; j < DC_C; ++j) u[j] = __shfl_sync(full, acc, j, 16);
         // S' = P(0, C) (.) S + sum_j w_j u_j^T
 #pragma unroll
         for (int i = 0; i < RPS; i += 4) {
