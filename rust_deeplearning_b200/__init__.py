@@ -4,9 +4,9 @@ From a model folder (config.json + safetensors) or a random-weights configuratio
 generated tokens: typed configuration and an architecture registry, weights by tensor name,
 layers put together from parts, a paged cache with a slot per sequence, one step function,
 a generation loop with seeded sampling, and hand-written CUDA kernels underneath.
-Four architectures are registered: Gemma 2, Ligirax, Dokulorn and Revepel.
+Five architectures are registered: Gemma 2, Ligirax, Dokulorn, Revepel and Gasetar.
 """
-from .config import dokulorn as _dokulorn, gemma2 as _gemma2, ligirax as _ligirax, revepel as _revepel  # registers the architectures
+from .config import dokulorn as _dokulorn, gasetar as _gasetar, gemma2 as _gemma2, ligirax as _ligirax, revepel as _revepel  # registers the architectures
 from .config.base import ConfigError, load_config, register_architecture, registered_architectures
 from .engine.api import Generator, load_model, random_model
 from .engine.generate import GenerationResult, generate

@@ -11,7 +11,7 @@ extern "C" {
 #define RDL_ACT_SILU 1
 #define RDL_ACT_SWISH_LIMIT 2   // min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1), L a parameter
 
-#define RDL_ABI_VERSION 18
+#define RDL_ABI_VERSION 19
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -93,6 +93,11 @@ int rdl_gated_activation(void* out, const void* gate_up, int dtype, int activati
 int rdl_softcap_inplace(void* z_f32, long long total, float cap, void* stream);
 int rdl_scale_inplace(void* z_f32, long long total, float scale, void* stream);
 int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long long total, void* stream);
+// The sum of a block whose sublayers read one norm, and the norm the next part asks for, in one pass over the rows:
+//   res <- res + scale * (a + b + c)     (b, c optional; the branches in branch_dtype, the sum in float, in that order)
+//   y   <- res / sqrt(mean(res^2) + eps) * (w + off)   in y_dtype, if y is given
+int rdl_add_branches_norm(float* res, const void* a, const void* b, const void* c, int branch_dtype, float scale, const void* w,
+                          int w_dtype, float eps, float off, void* y, int y_dtype, int n_rows, int width, void* stream);
 int rdl_convert_rows(void* out, int out_dtype, const void* in, int in_dtype, const int* row_index,
                      int n_rows, int width, void* stream);
 // A step's batch description from pinned host memory to the device, by a kernel (a copy engine's hand-over costs
@@ -116,6 +121,16 @@ int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, int n_token
                         int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq, const int* tok_pos,
                         int do_rope, float norm_eps, int norm_dim, int do_write, void* k_cache, void* v_cache,
                         const int* tables, int table_width, int page_size, int ring_pages, const int* seq_end, void* stream);
+
+// A norm over the whole query projection and over the whole key projection of a token (all heads at once, a weight
+// per column: wq [n_heads * head_dim], wk [n_kv_heads * head_dim], float), BEFORE the rotation, then the rotation and
+// the cache write as above:  q <- R(q / sqrt(sum(q^2) / q_count + eps) * wq), k likewise.  q_count, k_count: the
+// projections' sizes before any zero padding of their heads.
+int rdl_rope_projnorm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                            int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq, const int* tok_pos,
+                            int do_rope, const float* wq, const float* wk, float eps, int q_count, int k_count, int do_write,
+                            void* k_cache, void* v_cache, const int* tables, int table_width, int page_size, int ring_pages,
+                            const int* seq_end, void* stream);
 
 // ---- forms of the residual stream and of gates (csrc/rownorm.cu) ----
 // Norm after the sum: res <- norm(alpha * res + branch) with norm(v) = v / sqrt(mean(v^2) + eps) * (w + off), in float;
@@ -312,37 +327,44 @@ int rdl_latent_write(const LatentPrepareArgs* a, void* stream);
 int rdl_latent_assemble(void* out, int dtype, const void* rows, long long row_stride, int q_col, const void* kv,
                         const void* latent, int n_tokens, int n_heads, int dim, int rot_dim, int vdim, int kv_rank,
                         int pad, void* stream);
-// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]), out dense [tokens][heads * vdim]
+// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]), out dense [tokens][heads * vdim]; g_elem: a gate per value,
+// sigmoid(g[t, h * vdim + i])
 int rdl_gate_heads(void* out, int dtype, const void* in, long long in_stride, int in_head, const void* g, long long g_stride,
-                   int n_tokens, int n_heads, int vdim, void* stream);
-// a product per head: out[t, h, j] = sum_k w[h, j, k] x[t, h, k], optionally times sigmoid(gate[t, h])
+                   int n_tokens, int n_heads, int vdim, int g_elem, void* stream);
+// a product per head: out[t, h, j] = sum_k w[h, j, k] x[t, h, k], optionally times sigmoid(gate[t, h]) (gate_elem: of
+// gate[t, h * n_out + j])
 typedef struct {
     int dtype, n_tokens, n_heads, n_out, k;
     const void* x; long long x_stride; int x_head;
     const void* w;                             // [heads][n_out][k]
     void* out; long long out_stride; int out_head;
     const void* gate; long long gate_stride;   // optional
+    int gate_elem;
 } HeadsLinearArgs;
 int rdl_heads_linear(const HeadsLinearArgs* a, void* stream);
 
 // Decode attention of the absorbed form on tensor cores (csrc/latent_decode.cu): q [tokens][heads * width] attends over
 // the cached rows [pages][1][page_size][width] (bfloat16) as keys and, in their first kv_rank values, as values; the
 // first kv_rank values of every head of out [tokens][heads * width] are written.  n_splits blocks share a token's
-// keys (scratch of rdl_latent_decode_scratch_bytes when > 1).
+// keys (scratch of rdl_latent_decode_scratch_bytes when > 1).  sinks (optional, float [heads]): a logit per head without
+// key or value whose exponential joins the softmax's denominator once (not scaled).
 long long rdl_latent_decode_scratch_bytes(int n_tokens, int n_heads, int kv_rank, int n_splits);
 int rdl_latent_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* cache, const int* tables,
                       int table_width, int page_size, int ring_pages, const int* tok_seq, const int* tok_pos, int n_tokens,
                       int n_heads, int width, int kv_rank, float score_scale, int window, int max_keys, int n_splits,
-                      void* scratch, long long scratch_bytes, void* stream);
+                      void* scratch, long long scratch_bytes, const float* sinks, void* stream);
 
 // ---- routed feed-forward (csrc/moe.cu) ----
 // sel[t, k], sel_w[t, k]: the `top` experts of row t by softmax score + correction, and their softmax scores;
 // logits: float work space [rows][experts] (two kernels: the logits, then softmax and choice)
 // scoring: RDL_ROUTE_SOFTMAX, or RDL_ROUTE_SIGMOID (every expert's score is sigmoid(logit) by itself)
 #define RDL_ROUTE_SOFTMAX 0
+// RDL_ROUTE_SOFTMAX_CHOSEN: the choice is by the logits themselves and the weights are the softmax over the chosen
+// logits only.  bias (optional, float [experts]) is added to the logits before anything else, in every form.
 #define RDL_ROUTE_SIGMOID 1
-int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                  int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream);
+#define RDL_ROUTE_SOFTMAX_CHOSEN 2
+int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* bias, const float* correction, int n_rows,
+                  int n_experts, int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream);
 // mid[(t, k), :] = gated(W_gate[e] x_t, W_up[e] x_t) for e = sel[t, k] < n_real; w_gate_up [n_real][2 ff][width]
 // activation >= 16 (RDL_UNARY_*): experts of two matrices, mid = act(W_up[e] x_t) with w_gate_up [n_real][ff][width].
 // sel_w (optional): the pair's weight multiplies the expert's input, mid = f(W (sel_w[t, k] x_t)).

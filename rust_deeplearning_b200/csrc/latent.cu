@@ -261,14 +261,34 @@ __global__ void latent_assemble_vec_kernel(uint4* __restrict__ out, const T* __r
     }
 }
 
-// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]) in 16-byte pieces of bfloat16
+// out[t, h, :vdim] = in[t, h, :vdim] * sigmoid(g[t, h]) in 16-byte pieces of bfloat16 (g_elem: a gate per value,
+// g[t, h * vdim + i], read in 16-byte pieces too when g_vec)
 __global__ void gate_heads_vec_kernel(uint4* __restrict__ out, const __nv_bfloat16* __restrict__ in, long long in_stride, int in_head,
-                                      const __nv_bfloat16* __restrict__ g, long long g_stride, int n_tokens, int n_heads, int vdim) {
+                                      const __nv_bfloat16* __restrict__ g, long long g_stride, int n_tokens, int n_heads, int vdim,
+                                      int g_elem, int g_vec) {
     const int vp = vdim / 8;
     const long long total = (long long)n_tokens * n_heads * vp;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(idx / (n_heads * vp)), j = (int)(idx - (long long)t * n_heads * vp), h = j / vp, e = (j - h * vp) * 8;
-        const float gate = 1.0f / (1.0f + expf(-__bfloat162float(g[(long long)t * g_stride + h])));
+        float gate[8];
+        if (g_elem) {
+            const __nv_bfloat16* gp = g + (long long)t * g_stride + (long long)h * vdim + e;
+            if (g_vec) {
+                const uint4 graw = *reinterpret_cast<const uint4*>(gp);
+                const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(gh[i]); gate[2 * i] = v.x; gate[2 * i + 1] = v.y; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) gate[i] = __bfloat162float(gp[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gate[i] = 1.0f / (1.0f + expf(-gate[i]));
+        } else {
+            const float one = 1.0f / (1.0f + expf(-__bfloat162float(g[(long long)t * g_stride + h])));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gate[i] = one;
+        }
         const uint4 raw = *reinterpret_cast<const uint4*>(in + (long long)t * in_stride + (long long)h * in_head + e);
         const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
         uint4 res;
@@ -276,25 +296,26 @@ __global__ void gate_heads_vec_kernel(uint4* __restrict__ out, const __nv_bfloat
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 v = __bfloat1622float2(hp[i]);
-            rp[i] = __floats2bfloat162_rn(v.x * gate, v.y * gate);
+            rp[i] = __floats2bfloat162_rn(v.x * gate[2 * i], v.y * gate[2 * i + 1]);
         }
         out[idx] = res;
     }
 }
 
-// out[t, h, i] = in[t, h, i] * sigmoid(g[t, h]) for i < vdim: the output gate on the heads of an attention result.
+// out[t, h, i] = in[t, h, i] * sigmoid(g[t, h]) for i < vdim: the output gate on the heads of an attention result
+// (g_elem: a gate per value, g[t, h * vdim + i]).
 template <typename T>
 __global__ void gate_heads_kernel(T* __restrict__ out, const T* __restrict__ in, long long in_stride, int in_head,
-                                  const T* __restrict__ g, long long g_stride, int n_heads, int vdim) {
+                                  const T* __restrict__ g, long long g_stride, int n_heads, int vdim, int g_elem) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < n_heads * vdim; i += blockDim.x) {
         const int h = i / vdim, e = i - h * vdim;
-        const float gate = 1.0f / (1.0f + expf(-to_float(g[(long long)t * g_stride + h])));
+        const float gate = 1.0f / (1.0f + expf(-to_float(g[(long long)t * g_stride + (g_elem ? i : h)])));
         out[(long long)t * n_heads * vdim + i] = from_float<T>(to_float(in[(long long)t * in_stride + (long long)h * in_head + e]) * gate);
     }
 }
 
-// out[t, h, j] = sum_k w[h, j, k] x[t, h, k]  (times sigmoid(g[t, h]) if g is given): a product per head.
+// out[t, h, j] = sum_k w[h, j, k] x[t, h, k]  (times sigmoid(g[t, h]), or of g[t, h * n_out + j] with gate_elem, if g is given): a product per head.
 // One warp per (token, head, 32 consecutive j)?  No: a warp per (token tile, head, j) would re-read x; here a warp
 // takes one (head, j) for HL_ROWS tokens, lanes split k, so a weight row is read once for those tokens.  The sum
 // over k runs lane by lane in a fixed order and ends in a shuffle tree: it depends on k alone.
@@ -354,7 +375,7 @@ __global__ void __launch_bounds__(HL_WARPS * 32) heads_linear_kernel(HeadsLinear
         if (r >= rows) break;
         float v = warp_sum(acc[r]);
         if (lane == 0) {
-            if (a.gate) v *= 1.0f / (1.0f + expf(-to_float(((const T*)a.gate)[(long long)(t0 + r) * a.gate_stride + h])));
+            if (a.gate) v *= 1.0f / (1.0f + expf(-to_float(((const T*)a.gate)[(long long)(t0 + r) * a.gate_stride + (a.gate_elem ? h * a.n_out + j : h)])));
             ((T*)a.out)[(long long)(t0 + r) * a.out_stride + (long long)h * a.out_head + j] = from_float<T>(v);
         }
     }
@@ -435,7 +456,7 @@ extern "C" int rdl_latent_assemble(void* out, int dtype, const void* rows, long 
 }
 
 extern "C" int rdl_gate_heads(void* out, int dtype, const void* in, long long in_stride, int in_head, const void* g, long long g_stride,
-                              int n_tokens, int n_heads, int vdim, void* stream) {
+                              int n_tokens, int n_heads, int vdim, int g_elem, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "gate_heads: bad dtype %d", dtype);
     RDL_REQUIRE(out && in && g && n_heads > 0 && vdim > 0 && in_head >= vdim, "gate_heads: bad arguments");
     if (n_tokens == 0) return 0;
@@ -443,16 +464,17 @@ extern "C" int rdl_gate_heads(void* out, int dtype, const void* in, long long in
         const long long want = ((long long)n_tokens * n_heads * (vdim / 8) + 255) / 256;
         const unsigned blocks = (unsigned)(want > (long long)rdl_sm_count() * 16 ? (long long)rdl_sm_count() * 16 : want);
         gate_heads_vec_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)out, (const __nv_bfloat16*)in, in_stride, in_head,
-                                                                         (const __nv_bfloat16*)g, g_stride, n_tokens, n_heads, vdim);
+                                                                         (const __nv_bfloat16*)g, g_stride, n_tokens, n_heads, vdim, g_elem,
+                                                                         (int)(g_elem && g_stride % 8 == 0 && ((uintptr_t)g & 15) == 0));
         RDL_CHECK_LAUNCH("gate_heads");
         return 0;
     }
     if (dtype == RDL_BF16)
         gate_heads_kernel<__nv_bfloat16><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, in_stride, in_head,
-                                                                                      (const __nv_bfloat16*)g, g_stride, n_heads, vdim);
+                                                                                      (const __nv_bfloat16*)g, g_stride, n_heads, vdim, g_elem);
     else
         gate_heads_kernel<float><<<n_tokens, 256, 0, (cudaStream_t)stream>>>((float*)out, (const float*)in, in_stride, in_head, (const float*)g,
-                                                                              g_stride, n_heads, vdim);
+                                                                              g_stride, n_heads, vdim, g_elem);
     RDL_CHECK_LAUNCH("gate_heads");
     return 0;
 }

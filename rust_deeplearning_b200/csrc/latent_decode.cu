@@ -53,6 +53,7 @@ struct LatentDecodeArgs {
     float scale_log2;                                // score scale * log2(e)
     int tiles_per_split, n_splits;
     float* partial;                                  // [tokens][head groups * 16][splits][kv_rank + 2] (splits > 1)
+    const float* sinks;                              // optional [heads]: a logit that joins the denominator once, unscaled
 };
 
 // byte offset of 16-byte chunk c of a row whose chunk count is a multiple of 8 (every group of eight is swizzled)
@@ -266,7 +267,12 @@ __global__ void __launch_bounds__(LD_THREADS, 2) latent_decode_kernel(LatentDeco
         const int head = hg * LD_HEADS + g + 8 * r;
         if (head >= a.n_heads) continue;
         if (a.n_splits == 1) {
-            const float inv = 1.0f / l_run[r];
+            float l = l_run[r];
+            if (a.sinks) {      // base-2 domain, like m_run; with no key seen the sink alone fills the denominator and O is zero
+                const float sk = a.sinks[head] * 1.4426950408889634f;
+                l = m_run[r] == -INFINITY ? 1.0f : l + exp2f(sk - m_run[r]);
+            }
+            const float inv = 1.0f / l;
             __nv_bfloat16* dst = a.out + (long long)t * a.out_stride + (long long)head * width;
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
@@ -324,6 +330,7 @@ __global__ void __launch_bounds__(128) latent_decode_merge_kernel(LatentDecodeAr
         float L = 0.f;
         if (lane == 0)
             for (int s = 0; s < a.n_splits; ++s) L += factor[s];
+        if (lane == 0 && a.sinks) L = M == -INFINITY ? 1.0f : L + exp2f(a.sinks[head] * 1.4426950408889634f - M);
         L = __shfl_sync(0xffffffffu, L, 0);
         __syncwarp();
         factor[lane] = f[0] / L;
@@ -370,7 +377,7 @@ extern "C" long long rdl_latent_decode_scratch_bytes(int n_tokens, int n_heads, 
 extern "C" int rdl_latent_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* cache, const int* tables,
                                  int table_width, int page_size, int ring_pages, const int* tok_seq, const int* tok_pos, int n_tokens,
                                  int n_heads, int width, int kv_rank, float score_scale, int window, int max_keys, int n_splits,
-                                 void* scratch, long long scratch_bytes, void* stream) {
+                                 void* scratch, long long scratch_bytes, const float* sinks, void* stream) {
     RDL_REQUIRE(out && q && cache && tables && tok_seq && tok_pos, "latent_decode: missing operand");
     RDL_REQUIRE(width % 16 == 0 && width <= 640 && kv_rank % 16 == 0 && kv_rank > 0 && kv_rank <= 512 && kv_rank <= width,
                 "latent_decode: rows of %d values with %d latent values are not taken (multiples of 16 up to 640 and 512)", width, kv_rank);
@@ -387,7 +394,7 @@ extern "C" int rdl_latent_decode(void* out, long long out_stride, const void* q,
                 "latent_decode: scratch too small");
     LatentDecodeArgs a{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, out_stride, tok_seq, tok_pos, tables,
                        table_width, page_size, ring_pages, n_heads, width, kv_rank, window, score_scale * 1.4426950408889634f,
-                       (tiles + n_splits - 1) / n_splits, n_splits, (float*)scratch};
+                       (tiles + n_splits - 1) / n_splits, n_splits, (float*)scratch, sinks};
     const size_t smem = (size_t)LD_HEADS * width * 2 + LD_HEADS * LD_TILE * 2 + 2 * LD_WARPS * LD_HEADS * sizeof(float) + LD_TILE * sizeof(long long) +
                         (size_t)LD_TILE * width * 2 + 64;          // 64: a fragment load may reach past the last row's end
     const dim3 grid(n_splits, groups, n_tokens);

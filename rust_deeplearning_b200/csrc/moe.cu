@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(const T* _
 // softmax over a row's logits, choice = score + correction, the `top` largest choices: a warp per row
 constexpr int TOPK_WARPS = 4;
 
-__global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n_rows,
+__global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ bias,
+                                                                   const float* __restrict__ correction, int n_rows,
                                                                    int n_experts, int top, int scoring, int* __restrict__ sel,
                                                                    float* __restrict__ sel_w) {
     extern __shared__ float zs_all[];          // per warp: [n_experts] scores, [n_experts] choices
@@ -147,14 +148,17 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
     const float* zr = z + (long long)t * n_experts;
     float m = -INFINITY;
     float sum = 1.f;
-    if (scoring == RDL_ROUTE_SIGMOID) {
-        for (int e = lane; e < n_experts; e += 32) zs[e] = 1.0f / (1.0f + expf(-zr[e]));
+    auto logit = [&](int e) { return bias ? zr[e] + bias[e] : zr[e]; };
+    if (scoring == RDL_ROUTE_SOFTMAX_CHOSEN) {
+        for (int e = lane; e < n_experts; e += 32) zs[e] = logit(e);
+    } else if (scoring == RDL_ROUTE_SIGMOID) {
+        for (int e = lane; e < n_experts; e += 32) zs[e] = 1.0f / (1.0f + expf(-logit(e)));
     } else {
-        for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, zr[e]);
+        for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, logit(e));
         m = warp_max(m);
         sum = 0.f;
         for (int e = lane; e < n_experts; e += 32) {
-            const float p = expf(zr[e] - m);
+            const float p = expf(logit(e) - m);
             zs[e] = p;
             sum += p;
         }
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
     }
     __syncwarp();
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = scoring == RDL_ROUTE_SIGMOID ? zs[e] : zs[e] / sum;
+        const float s = scoring == RDL_ROUTE_SOFTMAX ? zs[e] / sum : zs[e];
         zs[e] = s;
         choice[e] = s + (correction ? correction[e] : 0.f);
     }
@@ -187,6 +191,14 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
             choice[best_e] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (scoring == RDL_ROUTE_SOFTMAX_CHOSEN && lane == 0) {
+        // the weights: a softmax over the chosen logits alone (the first chosen is the largest), summed in the order of the choice
+        float* w = sel_w + (long long)t * top;
+        const float top_logit = w[0];
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - top_logit); total += w[k]; }
+        for (int k = 0; k < top; ++k) w[k] /= total;
     }
 }
 
@@ -438,12 +450,12 @@ __global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_b
 
 }  // namespace
 
-extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int n_rows, int n_experts,
-                             int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream) {
+extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, const float* bias, const float* correction, int n_rows,
+                             int n_experts, int width, int top, int scoring, int* sel, float* sel_w, float* logits, void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "moe_route: bad dtype %d", dtype);
     RDL_REQUIRE(x && w_router && sel && sel_w && logits && n_experts > 0 && width > 0, "moe_route: bad arguments");
     RDL_REQUIRE(top >= 1 && top <= n_experts, "moe_route: %d of %d experts cannot be chosen", top, n_experts);
-    RDL_REQUIRE(scoring == RDL_ROUTE_SOFTMAX || scoring == RDL_ROUTE_SIGMOID, "moe_route: unknown scoring %d", scoring);
+    RDL_REQUIRE(scoring == RDL_ROUTE_SOFTMAX || scoring == RDL_ROUTE_SIGMOID || scoring == RDL_ROUTE_SOFTMAX_CHOSEN, "moe_route: unknown scoring %d", scoring);
     RDL_REQUIRE(n_experts <= 1024, "moe_route: %d experts exceed the 1,024 the router kernels hold", n_experts);
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -463,7 +475,7 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
     }
     const size_t smem = (size_t)TOPK_WARPS * 2 * n_experts * sizeof(float);
     RDL_CHECK_EX(rdl_launch(moe_topk_kernel, dim3((n_rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(TOPK_WARPS * 32), smem, st, (const float*)logits,
-                            correction, n_rows, n_experts, top, scoring, sel, sel_w), "moe_route");
+                            bias, correction, n_rows, n_experts, top, scoring, sel, sel_w), "moe_route");
     return 0;
 }
 

@@ -385,6 +385,148 @@ __global__ void __launch_bounds__(256) rope_norm_cache_vec_kernel(T* __restrict_
     }
 }
 
+// A root-mean-square norm over the WHOLE query projection and over the WHOLE key projection of a token (all heads at
+// once, one learned weight per column), then the rotation, then the cache write, in one pass over packed rows:
+//     q <- R_pos(q / sqrt(sum(q^2) / q_count + eps) * wq),   k likewise with wk and k_count;   values are copied.
+// q_count / k_count: the projections' true sizes (heads laid out with zero padding count their unpadded values).
+// One block per token.  First the two sums of squares (lane by lane, across each warp, then the warps' parts in rising
+// order: the order depends on the sizes alone), then a work item per rotated pair of pieces, per piece that does not
+// rotate and per value piece; all in float, every value rounded once on the way back into the row and into the cache.
+// VEC: pieces of 16 bytes (head_dim and rotary_dim / 2 whole numbers of them), else single values.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) rope_projnorm_cache_kernel(T* __restrict__ rows, long long row_stride, int n_heads, int n_kv_heads,
+                                                                  int head_dim, int rotary_dim, const float* __restrict__ cos_t,
+                                                                  const float* __restrict__ sin_t, const int* __restrict__ tok_seq,
+                                                                  const int* __restrict__ tok_pos, int do_rope, const float* __restrict__ wq,
+                                                                  const float* __restrict__ wk, float eps, float q_count, float k_count,
+                                                                  int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                                  const int* __restrict__ tables, int table_width, int page_size,
+                                                                  int ring_pages, const int* __restrict__ seq_end) {
+    constexpr int N = VEC ? Chunk<T>::N : 1;
+    __shared__ float part[2][8];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    if (pos < 0) return;  // a padding row of a fixed-size batch
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    T* row = rows + (long long)t * row_stride;
+    const int qw = n_heads * head_dim, kw = n_kv_heads * head_dim;
+    auto load = [](const T* p, float (&f)[N]) {
+        if constexpr (VEC) Chunk<T>::load(p, f);
+        else f[0] = to_float(*p);
+    };
+    auto store = [](T* p, const float (&f)[N]) {
+        if constexpr (VEC) *reinterpret_cast<uint4*>(p) = Chunk<T>::pack(f);
+        else *p = from_float<T>(f[0]);
+    };
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x * N; i < qw + kw; i += blockDim.x * N) {
+        float f[N];
+        load(row + i, f);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < N; ++j) s = fmaf(f[j], f[j], s);
+        if (i < qw) sq += s; else sk += s;
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) { part[0][warp] = sq; part[1][warp] = sk; }
+    __syncthreads();
+    sq = sk = 0.f;
+    for (int w = 0; w < n_warps; ++w) { sq += part[0][w]; sk += part[1][w]; }
+    const float inv_q = 1.0f / sqrtf(sq / q_count + eps), inv_k = k_count > 0.f ? 1.0f / sqrtf(sk / k_count + eps) : 0.f;
+
+    bool write = do_write && n_kv_heads > 0;
+    const int seq = tok_seq[t];
+    // In a ring a later token of this step may land on the same row: only the last writer writes.
+    if (write && (long long)pos + (long long)ring_pages * page_size < (long long)seq_end[seq]) write = false;
+    const int r = pos % page_size;
+    const int half = do_rope ? rotary_dim >> 1 : 0;
+    const int chunks = head_dim / N, hc = half / N;
+    const int per_head = chunks - hc;                      // pairs, then pieces that do not rotate
+    const int qk_items = (n_heads + n_kv_heads) * per_head;
+    const int total = qk_items + (write ? n_kv_heads * chunks : 0);
+    const int* table = tables + (long long)seq * table_width;
+    for (int it = threadIdx.x; it < total; it += blockDim.x) {
+        if (it >= qk_items) {                              // a piece of a value head, copied as it is
+            const int v = it - qk_items, head = v / chunks, c = v - head * chunks;
+            float f[N];
+            load(row + qw + kw + head * head_dim + c * N, f);
+            T* dst = v_cache + rdl_cache_offset(table, pos, page_size, ring_pages, n_kv_heads, head, head_dim);
+            store(dst + (VEC ? rdl_swizzled_chunk(r, c, chunks) * N : rdl_cache_col<T>(r, c, head_dim)), f);
+            continue;
+        }
+        const int head = it / per_head, j = it - head * per_head;
+        const bool is_q = head < n_heads;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? wq + head * head_dim : wk + (head - n_heads) * head_dim;
+        T* hrow = row + head * head_dim;
+        T* dst = (write && !is_q) ? k_cache + rdl_cache_offset(table, pos, page_size, ring_pages, n_kv_heads, head - n_heads, head_dim) : nullptr;
+        auto place = [&](int c) { return VEC ? rdl_swizzled_chunk(r, c, chunks) * N : rdl_cache_col<T>(r, c, head_dim); };
+        if (j < hc) {
+            const int i0 = j * N;
+            float a[N], b[N];
+            load(hrow + i0, a);
+            load(hrow + i0 + half, b);
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                const float u = a[e] * inv * w[i0 + e], v = b[e] * inv * w[i0 + half + e];
+                const float cs = cos_t[(long long)pos * half + i0 + e], sn = sin_t[(long long)pos * half + i0 + e];
+                a[e] = u * cs - v * sn;
+                b[e] = v * cs + u * sn;
+            }
+            store(hrow + i0, a);
+            store(hrow + i0 + half, b);
+            if (dst) { store(dst + place(j), a); store(dst + place(j + hc), b); }
+        } else {
+            const int c = j + hc, i0 = c * N;
+            float a[N];
+            load(hrow + i0, a);
+#pragma unroll
+            for (int e = 0; e < N; ++e) a[e] = a[e] * inv * w[i0 + e];
+            store(hrow + i0, a);
+            if (dst) store(dst + place(c), a);
+        }
+    }
+}
+
+extern "C" int rdl_rope_projnorm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                       int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq,
+                                       const int* tok_pos, int do_rope, const float* wq, const float* wk, float eps, int q_count,
+                                       int k_count, int do_write, void* k_cache, void* v_cache, const int* tables, int table_width,
+                                       int page_size, int ring_pages, const int* seq_end, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "rope_projnorm_cache: bad dtype %d", dtype);
+    RDL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads >= 0 && head_dim > 0 && head_dim <= 4096,
+                "rope_projnorm_cache: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d", n_tokens, n_heads, n_kv_heads, head_dim);
+    RDL_REQUIRE(row_stride >= (long long)(n_heads + 2 * n_kv_heads) * head_dim, "rope_projnorm_cache: the row stride is below the heads' width");
+    RDL_REQUIRE(!do_rope || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim && cos_table && sin_table),
+                "rope_projnorm_cache: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    RDL_REQUIRE(wq && (wk || n_kv_heads == 0) && eps > 0.f && q_count > 0 && q_count <= n_heads * head_dim &&
+                    (n_kv_heads == 0 || (k_count > 0 && k_count <= n_kv_heads * head_dim)),
+                "rope_projnorm_cache: the norms need weights, eps > 0 and the projections' true sizes");
+    RDL_REQUIRE(tok_seq && tok_pos, "rope_projnorm_cache: missing batch description");
+    RDL_REQUIRE(!do_write || n_kv_heads == 0 ||
+                    (k_cache && v_cache && tables && seq_end && page_size > 0 && ring_pages > 0 && ring_pages <= table_width),
+                "rope_projnorm_cache: cache write needs storage, page tables and lengths");
+    if (n_tokens == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int per_chunk = dtype == RDL_BF16 ? 8 : 4;
+    const int half = do_rope ? rotary_dim / 2 : 0;
+    const bool vec = head_dim % per_chunk == 0 && half % per_chunk == 0 && row_stride % per_chunk == 0 &&
+                     (((uintptr_t)rows | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+    cudaError_t e;
+#define RDL_PROJNORM(T, V)                                                                                                               \
+    e = rdl_launch(rope_projnorm_cache_kernel<T, V>, dim3(n_tokens), dim3(256), 0, st, (T*)rows, row_stride, n_heads, n_kv_heads, head_dim, \
+                   rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, wq, wk, eps, (float)q_count, (float)k_count, do_write,   \
+                   (T*)k_cache, (T*)v_cache, tables, table_width, page_size, ring_pages, seq_end)
+    if (dtype == RDL_BF16) { if (vec) RDL_PROJNORM(__nv_bfloat16, true); else RDL_PROJNORM(__nv_bfloat16, false); }
+    else { if (vec) RDL_PROJNORM(float, true); else RDL_PROJNORM(float, false); }
+#undef RDL_PROJNORM
+    RDL_CHECK_EX(e, "rope_projnorm_cache");
+    return 0;
+}
+
 extern "C" int rdl_rope_norm_cache(void* rows, long long row_stride, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                    int rotary_dim, const float* cos_table, const float* sin_table, const int* tok_seq,
                                    const int* tok_pos, int do_rope, float norm_eps, int norm_dim, int do_write, void* k_cache,

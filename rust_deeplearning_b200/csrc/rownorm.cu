@@ -478,3 +478,120 @@ extern "C" int rdl_group_norm_gate(void* out, int out_dtype, const float* x, int
     RDL_CHECK_EX(e, "group_norm_gate");
     return 0;
 }
+
+// ---- the sum of a block whose sublayers read one norm, with the norm the next part asks for ----
+// res <- res + scale * (a + b + c) (b, c optional), then y <- norm(res) if y is given.  The branches are added up in
+// float in the order a, b, c; a row's sum of squares is formed in an order that depends on its width alone.
+template <typename TB, typename TY, int NIT>
+__global__ void __launch_bounds__(256) add_branches_norm_vec_kernel(float* __restrict__ res, const TB* __restrict__ a, const TB* __restrict__ b,
+                                                                    const TB* __restrict__ c, float scale, const void* __restrict__ w,
+                                                                    int w_dtype, float eps, float off, TY* __restrict__ y, int width) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const long long base = (long long)blockIdx.x * width;
+    float h[NIT][4], av[NIT][4], bv[NIT][4], cv[NIT][4];
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+            rn_load4(res + base + e, h[it]);
+            rn_load4(a + base + e, av[it]);
+            if (b) rn_load4(b + base + e, bv[it]);
+            if (c) rn_load4(c + base + e, cv[it]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float s = av[it][k];
+                if (b) s += bv[it][k];
+                if (c) s += cv[it][k];
+                h[it][k] = fmaf(scale, s, h[it][k]);
+                ss = fmaf(h[it][k], h[it][k], ss);
+            }
+            rn_store4(res + base + e, h[it]);
+        }
+    }
+    if (!y) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+        const int e = (threadIdx.x + it * blockDim.x) * 4;
+        if (e < width) {
+            float wv[4], v[4];
+            rn_load4(w, e, w_dtype, wv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = h[it][k] * inv * (wv[k] + off);
+            rn_store4(y + base + e, v);
+        }
+    }
+}
+
+template <typename TB, typename TY>
+__global__ void add_branches_norm_kernel(float* __restrict__ res, const TB* __restrict__ a, const TB* __restrict__ b, const TB* __restrict__ c,
+                                         float scale, const void* __restrict__ w, int w_dtype, float eps, float off, TY* __restrict__ y,
+                                         int width) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const long long base = (long long)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float s = to_float(a[base + i]);
+        if (b) s += to_float(b[base + i]);
+        if (c) s += to_float(c[base + i]);
+        const float h = fmaf(scale, s, res[base + i]);
+        res[base + i] = h;            // this thread reads it back below
+        ss = fmaf(h, h, ss);
+    }
+    if (!y) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        y[base + i] = from_float<TY>(res[base + i] * inv * (rdl_load(w, i, w_dtype) + off));
+}
+
+extern "C" int rdl_add_branches_norm(float* res, const void* a, const void* b, const void* c, int branch_dtype, float scale, const void* w,
+                                     int w_dtype, float eps, float off, void* y, int y_dtype, int n_rows, int width, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(branch_dtype) && rdl_valid_dtype(w_dtype) && rdl_valid_dtype(y_dtype), "add_branches_norm: bad dtype");
+    RDL_REQUIRE(res && a && n_rows >= 0 && width > 0 && (!y || w), "add_branches_norm: missing rows, branch or weight");
+    if (n_rows == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    const int vt = vec_threads(width);
+    const dim3 grid(n_rows);
+    const bool vec = vec_ok(width, vt) && aligned16(res) && aligned16(a) && aligned16(b) && aligned16(c) && aligned16(w) && aligned16(y);
+    const int depth = vec_depth(width, vt);
+#define ABN_VEC(TB, TY, N) \
+    e = rdl_launch(add_branches_norm_vec_kernel<TB, TY, N>, grid, dim3(vt), 0, st, res, (const TB*)a, (const TB*)b, (const TB*)c, scale, w, w_dtype, eps, off, (TY*)y, width)
+#define ABN_LAUNCH(N)                                                                       \
+    do {                                                                                    \
+        if (branch_dtype == RDL_BF16) {                                                     \
+            if (y_dtype == RDL_BF16) ABN_VEC(__nv_bfloat16, __nv_bfloat16, N);              \
+            else ABN_VEC(__nv_bfloat16, float, N);                                          \
+        } else {                                                                            \
+            if (y_dtype == RDL_BF16) ABN_VEC(float, __nv_bfloat16, N);                      \
+            else ABN_VEC(float, float, N);                                                  \
+        }                                                                                   \
+    } while (0)
+#define ABN_PLAIN(TB, TY) \
+    e = rdl_launch(add_branches_norm_kernel<TB, TY>, grid, dim3(row_threads(width)), 0, st, res, (const TB*)a, (const TB*)b, (const TB*)c, scale, w, w_dtype, eps, off, (TY*)y, width)
+    if (vec) {
+        RN_BY_DEPTH(depth, ABN_LAUNCH)
+    } else if (branch_dtype == RDL_BF16) {
+        if (y_dtype == RDL_BF16) ABN_PLAIN(__nv_bfloat16, __nv_bfloat16); else ABN_PLAIN(__nv_bfloat16, float);
+    } else {
+        if (y_dtype == RDL_BF16) ABN_PLAIN(float, __nv_bfloat16); else ABN_PLAIN(float, float);
+    }
+#undef ABN_VEC
+#undef ABN_LAUNCH
+#undef ABN_PLAIN
+    RDL_CHECK_EX(e, "add_branches_norm");
+    return 0;
+}

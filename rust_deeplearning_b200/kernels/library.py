@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 18
+ABI_VERSION = 19
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -233,7 +233,7 @@ class HeadsLinearArgs(ctypes.Structure):
         ("x", ctypes.c_void_p), ("x_stride", ctypes.c_longlong), ("x_head", ctypes.c_int),
         ("w", ctypes.c_void_p),
         ("out", ctypes.c_void_p), ("out_stride", ctypes.c_longlong), ("out_head", ctypes.c_int),
-        ("gate", ctypes.c_void_p), ("gate_stride", ctypes.c_longlong),
+        ("gate", ctypes.c_void_p), ("gate_stride", ctypes.c_longlong), ("gate_elem", ctypes.c_int),
     ]
 
 
@@ -304,6 +304,8 @@ _SIGNATURES = {
     "rdl_convert_rows": [_P, _I, _P, _I, _P, _I, _I, _P],
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
     "rdl_rope_norm_cache": [_P, _LL, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _F, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
+    "rdl_rope_projnorm_cache": [_P, _LL, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
+    "rdl_add_branches_norm": [_P, _P, _P, _P, _I, _F, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "rdl_postnorm": [_P, _P, _I, _F, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "rdl_norm_pair": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _I, _I, _P],
     "rdl_gate_mul": [_P, _LL, _P, _LL, _P, _LL, _I, _I, _I, _I, _P],
@@ -330,10 +332,10 @@ _SIGNATURES = {
     "rdl_latent_prepare": [ctypes.POINTER(LatentPrepareArgs), _P],
     "rdl_latent_write": [ctypes.POINTER(LatentPrepareArgs), _P],
     "rdl_latent_assemble": [_P, _I, _P, _LL, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "rdl_gate_heads": [_P, _I, _P, _LL, _I, _P, _LL, _I, _I, _I, _P],
+    "rdl_gate_heads": [_P, _I, _P, _LL, _I, _P, _LL, _I, _I, _I, _I, _P],
     "rdl_heads_linear": [ctypes.POINTER(HeadsLinearArgs), _P],
-    "rdl_latent_decode": [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _LL, _P],
-    "rdl_moe_route": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "rdl_latent_decode": [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _LL, _P, _P],
+    "rdl_moe_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "rdl_moe_gate_up": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "rdl_moe_down_combine": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "rdl_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P],

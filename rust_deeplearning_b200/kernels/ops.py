@@ -199,6 +199,32 @@ def postnorm_(residual: torch.Tensor, branch: torch.Tensor, norm: NormParams, al
     return y
 
 
+def add_branches_norm_(residual: torch.Tensor, branches, scale: float, norm: Optional[NormParams] = None,
+                       out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """The sum of a block whose sublayers read one norm, in place on the float32 stream:
+    residual <- residual + scale * (b0 + b1 + b2) for one to three branches of one dtype (added up in float, in that
+    order); with `norm`, also returns rms_norm(residual; norm) in out_dtype, from the same pass over the rows."""
+    branches = [b for b in branches if b is not None]
+    _need(1 <= len(branches) <= 3, "add_branches_norm_: one to three branches")
+    _need(residual.dtype is torch.float32 and residual.is_contiguous() and residual.dim() == 2,
+          "add_branches_norm_: the stream is a contiguous float32 [rows, width] tensor")
+    for b in branches:
+        _need(b.is_contiguous() and b.shape == residual.shape and b.dtype is branches[0].dtype,
+              "add_branches_norm_: the branches must have the stream's shape and one dtype")
+    rows, width = residual.shape
+    y = None
+    if norm is not None:
+        _need(norm.weight.is_contiguous() and norm.weight.numel() == width, f"add_branches_norm_: the norm's weight must hold {width} values")
+        y = torch.empty((rows, width), dtype=out_dtype or branches[0].dtype, device=residual.device)
+    b = branches + [None, None]
+    library.check(library.load().rdl_add_branches_norm(
+        _ptr(residual), _ptr(b[0]), _ptr(b[1]), _ptr(b[2]), _dtype_code(b[0]), float(scale),
+        _ptr(norm.weight) if norm is not None else None, _dtype_code(norm.weight) if norm is not None else 0,
+        float(norm.eps) if norm is not None else 0.0, float(norm.offset) if norm is not None else 0.0,
+        _ptr(y), _dtype_code(y) if y is not None else 0, rows, width, _stream(residual)))
+    return y
+
+
 def norm_pair(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, factor: float) -> torch.Tensor:
     """float32 factor * (rms_norm(a; wa) + rms_norm(b; wb)), both norms with plain weights."""
     _need(a.dim() == 2 and a.shape == b.shape and a.dtype is b.dtype and a.is_contiguous() and b.is_contiguous(),
@@ -589,6 +615,45 @@ def rope_norm_cache(rows: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
     return rows
 
 
+def rope_projnorm_cache(rows: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, *, tok_seq, tok_pos, wq: torch.Tensor,
+                        wk: Optional[torch.Tensor], eps: float, q_count: int, k_count: int, cos: Optional[torch.Tensor] = None,
+                        sin: Optional[torch.Tensor] = None, rotary_dim: int = 0, pages: Optional[KVPages] = None,
+                        seq_end: Optional[torch.Tensor] = None):
+    """In place on packed rows [tokens, >= (n_heads + 2 n_kv_heads) * head_dim]: a root-mean-square norm over a token's
+    WHOLE query projection and over its WHOLE key projection (all heads at once; float32 weights wq [n_heads * head_dim],
+    wk [n_kv_heads * head_dim], one per column), then the rotation of every query and key head by the tables (if given),
+    all in float and rounded once; key and value rows then go to the cache (if `pages` is given).
+    q_count, k_count: the projections' sizes without any zero padding of their heads (what the mean divides by)."""
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[1] >= (n_heads + 2 * n_kv_heads) * head_dim,
+          "rope_projnorm_cache: packed rows narrower than the heads")
+    T = rows.shape[0]
+    _int32(tok_pos, "tok_pos", T)
+    _int32(tok_seq, "tok_seq", T)
+    _need(wq.dtype is torch.float32 and wq.is_contiguous() and wq.numel() == n_heads * head_dim,
+          "rope_projnorm_cache: the query norm's weight must be float32 [n_heads * head_dim]")
+    _need(n_kv_heads == 0 or (wk is not None and wk.dtype is torch.float32 and wk.is_contiguous() and wk.numel() == n_kv_heads * head_dim),
+          "rope_projnorm_cache: the key norm's weight must be float32 [n_kv_heads * head_dim]")
+    do_rope = cos is not None
+    if do_rope:
+        _need(cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+              and cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim, "rotary tables must be float32 [positions, rotary_dim/2]")
+    do_write = pages is not None and n_kv_heads > 0
+    if do_write:
+        _need(pages.k.dtype is rows.dtype and pages.v.dtype is rows.dtype, "cache dtype differs from the activations'")
+        _need(tuple(pages.k.shape[1:]) == (n_kv_heads, pages.page_size, head_dim) and pages.k.is_contiguous()
+              and pages.v.is_contiguous() and pages.v.shape == pages.k.shape, "cache storage has the wrong shape")
+        _int32(pages.tables, "page tables")
+        _int32(seq_end, "seq_end")
+    library.check(library.load().rdl_rope_projnorm_cache(
+        _ptr(rows), rows.stride(0), _dtype_code(rows), T, n_heads, n_kv_heads, head_dim, rotary_dim if do_rope else 0,
+        _ptr(cos), _ptr(sin), _ptr(tok_seq), _ptr(tok_pos), int(do_rope), _ptr(wq), _ptr(wk), float(eps), int(q_count), int(k_count),
+        int(do_write), _ptr(pages.k) if do_write else None, _ptr(pages.v) if do_write else None,
+        _ptr(pages.tables) if do_write else None, pages.tables.shape[1] if do_write else 0,
+        pages.page_size if do_write else 0, pages.ring_pages if do_write else 0,
+        _ptr(seq_end) if do_write else None, _stream(rows)))
+    return rows
+
+
 PREFILL_QUERY_TILE = 64    # query rows of a tile in the lists the prefill attention kernels take
 
 
@@ -895,11 +960,13 @@ def latent_assemble(rows: torch.Tensor, q_col: int, kv: torch.Tensor, latent: to
 
 
 def gate_heads(x: torch.Tensor, head_stride: int, gate: torch.Tensor, n_heads: int, vdim: int,
-               row_stride: Optional[int] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+               row_stride: Optional[int] = None, n_rows: Optional[int] = None, per_value: bool = False) -> torch.Tensor:
     """[tokens, n_heads * vdim] = x[t * row_stride + h * head_stride + i] * sigmoid(gate[t, h]) for i < vdim; `gate` may be
-    a column slice of wider rows.  By default x is [tokens, ...] and row_stride its row stride; with row_stride and n_rows
+    a column slice of wider rows.  per_value: a gate for every value, sigmoid(gate[t, h * vdim + i]).  By default x is
+    [tokens, ...] and row_stride its row stride; with row_stride and n_rows
     given x is any dense tensor addressed by the two strides (head-major results of a batched product, say)."""
-    _need(gate.dim() == 2 and gate.stride(1) == 1 and gate.dtype is x.dtype and gate.shape[1] >= n_heads, "gate_heads: bad gate")
+    _need(gate.dim() == 2 and gate.stride(1) == 1 and gate.dtype is x.dtype and gate.shape[1] >= n_heads * (vdim if per_value else 1),
+          "gate_heads: bad gate")
     if row_stride is None:
         _need(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= (n_heads - 1) * head_stride + vdim, "gate_heads: shapes do not fit")
         T, row_stride = x.shape[0], x.stride(0)
@@ -909,14 +976,15 @@ def gate_heads(x: torch.Tensor, head_stride: int, gate: torch.Tensor, n_heads: i
         T = n_rows
     out = torch.empty((T, n_heads * vdim), dtype=x.dtype, device=x.device)
     library.check(library.load().rdl_gate_heads(_ptr(out), _dtype_code(out), _ptr(x), row_stride, head_stride, _ptr(gate), gate.stride(0),
-                                                T, n_heads, vdim, _stream(x)))
+                                                T, n_heads, vdim, int(bool(per_value)), _stream(x)))
     return out
 
 
 def heads_linear(x: torch.Tensor, x_col: int, x_head: int, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_col: int = 0,
-                 out_head: Optional[int] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out_head: Optional[int] = None, gate: Optional[torch.Tensor] = None, gate_per_value: bool = False) -> torch.Tensor:
     """A product per head: out[t, out_col + h * out_head + j] = sum_k w[h, j, k] * x[t, x_col + h * x_head + k], optionally
-    times sigmoid(gate[t, h]).  w: [heads, n_out, k].  Without `out` the result is dense [tokens, heads * n_out]."""
+    times sigmoid(gate[t, h]) (gate_per_value: of gate[t, h * n_out + j]).  w: [heads, n_out, k].  Without `out` the
+    result is dense [tokens, heads * n_out]."""
     _need(x.dim() == 2 and x.stride(1) == 1 and w.dim() == 3 and w.is_contiguous() and w.dtype is x.dtype, "heads_linear: bad operands")
     H, n_out, k = w.shape
     T = x.shape[0]
@@ -933,8 +1001,9 @@ def heads_linear(x: torch.Tensor, x_col: int, x_head: int, w: torch.Tensor, out:
     a.w = w.data_ptr()
     a.out, a.out_stride, a.out_head = out.data_ptr() + out_col * es, out.stride(0), out_head
     if gate is not None:
-        _need(gate.dtype is x.dtype and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[1] >= H, "heads_linear: bad gate")
-        a.gate, a.gate_stride = gate.data_ptr(), gate.stride(0)
+        _need(gate.dtype is x.dtype and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[1] >= H * (n_out if gate_per_value else 1),
+              "heads_linear: bad gate")
+        a.gate, a.gate_stride, a.gate_elem = gate.data_ptr(), gate.stride(0), int(bool(gate_per_value))
     library.check(library.load().rdl_heads_linear(ctypes.byref(a), _stream(x)))
     return out
 
@@ -946,12 +1015,16 @@ def latent_decode_ok(dtype, width: int, kv_rank: int, page_size: int) -> bool:
 
 
 def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads: int, kv_rank: int, score_scale: float,
-                  window: Optional[int], scratch=None, n_splits: Optional[int] = None) -> torch.Tensor:
+                  window: Optional[int], scratch=None, n_splits: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-token attention of the absorbed form: q [tokens, n_heads * width] (width = kv_rank + rot_dim) over the
     cached rows `pages.k` [pages, 1, page_size, width], which are keys and, in their first kv_rank values, values.
     Returns [tokens, n_heads * width] whose first kv_rank values per head hold the result (the rest is not written).
-    scratch: callable(nbytes) -> float32 tensor for the partial results when a token's keys are shared between blocks."""
+    scratch: callable(nbytes) -> float32 tensor for the partial results when a token's keys are shared between blocks.
+    sinks: float32 [n_heads] - a logit per head without key or value whose exponential joins the denominator once."""
     _dense(q, "q")
+    if sinks is not None:
+        _need(sinks.dtype is torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads and sinks.device == q.device,
+              "latent_decode: sinks must be float32 [n_heads]")
     T = q.shape[0]
     width = pages.k.shape[3]
     _need(q.dtype is torch.bfloat16 and pages.k.dtype is torch.bfloat16 and q.shape[1] == n_heads * width
@@ -972,7 +1045,7 @@ def latent_decode(q: torch.Tensor, b: AttentionBatch, pages: KVPages, *, n_heads
     library.check(lib.rdl_latent_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(pages.k), _ptr(pages.tables), pages.tables.shape[1],
                                         pages.page_size, pages.ring_pages, _ptr(b.tok_seq), _ptr(b.tok_pos), b.n_tokens, n_heads, width,
                                         kv_rank, float(score_scale), int(window or 0), max(b.max_keys, 1), splits, _ptr(buf),
-                                        buf.numel() * 4 if buf is not None else 0, _stream(q)), 2 if splits > 1 else 1)
+                                        buf.numel() * 4 if buf is not None else 0, _ptr(sinks), _stream(q)), 2 if splits > 1 else 1)
     return out
 
 
@@ -988,23 +1061,27 @@ UNARY_FORMS = {"relu2": 16, "silu_plain": 17}
 EXPERT_FORMS = dict(GATED_FORMS, **UNARY_FORMS)
 
 
-ROUTE_SCORING = {"softmax": 0, "sigmoid": 1}     # `csrc/api.h`, RDL_ROUTE_*
+ROUTE_SCORING = {"softmax": 0, "sigmoid": 1, "softmax_chosen": 2}     # `csrc/api.h`, RDL_ROUTE_*
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scoring: str = "softmax"):
-    """Per row: scores of all experts from the float32 logits W_r x (softmax over the experts, or sigmoid expert by
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scoring: str = "softmax",
+              bias: Optional[torch.Tensor] = None):
+    """Per row: scores of all experts from the float32 logits W_r x + bias (softmax over the experts, or sigmoid expert by
     expert); the `top` experts with the largest score + correction (int32 [rows, top]) and their scores without it
-    (float32 [rows, top])."""
+    (float32 [rows, top]).  scoring "softmax_chosen": the choice is by the logits themselves and the weights are the
+    softmax over the chosen logits only."""
     _need(scoring in ROUTE_SCORING, f"moe_route: unknown scoring '{scoring}', known: {sorted(ROUTE_SCORING)}")
     _dense(x, "x")
     _need(w_router.dtype is torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1], "moe_route: float32 router [experts, width]")
     E = w_router.shape[0]
     if correction is not None:
         _need(correction.dtype is torch.float32 and correction.is_contiguous() and correction.numel() == E, "moe_route: float32 correction [experts]")
+    if bias is not None:
+        _need(bias.dtype is torch.float32 and bias.is_contiguous() and bias.numel() == E, "moe_route: float32 bias [experts]")
     sel = torch.empty((x.shape[0], top), dtype=torch.int32, device=x.device)
     sel_w = torch.empty((x.shape[0], top), dtype=torch.float32, device=x.device)
     logits = torch.empty((x.shape[0], E), dtype=torch.float32, device=x.device)
-    library.check(library.load().rdl_moe_route(_ptr(x), _dtype_code(x), _ptr(w_router), _ptr(correction), x.shape[0], E, x.shape[1], top,
+    library.check(library.load().rdl_moe_route(_ptr(x), _dtype_code(x), _ptr(w_router), _ptr(bias), _ptr(correction), x.shape[0], E, x.shape[1], top,
                                                ROUTE_SCORING[scoring], _ptr(sel), _ptr(sel_w), _ptr(logits), _stream(x)), 2)
     return sel, sel_w
 

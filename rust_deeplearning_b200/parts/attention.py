@@ -13,6 +13,9 @@ Interface of a mixer:
 
 Optional parameters, for designs that have them (the reference's attention has none of these):
   qk_norm_eps  after rotation every query and key head is divided by its root mean square (no weight), in float
+  proj_norm_eps  BEFORE rotation a token's whole query projection, all heads at once, is divided by its root mean square
+               and multiplied by a learned weight per column, and its whole key projection likewise (tensor roles
+               "q_norm" [n_heads * head_dim] and "k_norm" [n_kv_heads * head_dim]), in float
   sinks        a learned logit per query head without key or value: exp(sink_h) joins the softmax's denominator once
   gate         "sigmoid": the concatenated heads are multiplied element by element by sigmoid(W_g x) before W_o
   value_dim    values of another size than keys
@@ -47,7 +50,7 @@ class Attention:
 
     def __init__(self, *, hidden_size, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, position,
                  wq, wk, wv, wo, value_dim=None, qk_norm_eps=None, sinks=None, gate=None, wg=None, score_bias=None,
-                 cache_window=None):
+                 cache_window=None, proj_norm_eps=None, q_norm=None, k_norm=None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
         value_dim = head_dim if value_dim is None else value_dim
@@ -57,15 +60,33 @@ class Attention:
             self.cache_window = window if cache_window is None else int(cache_window)
             if self.cache_window < window:
                 raise ValueError(f"attention: the cache keeps {self.cache_window} keys, the window spans {window}")
-        if score_bias is not None and (sinks is not None or qk_norm_eps is not None or gate is not None):
+        if (proj_norm_eps is None) != (q_norm is None) or (q_norm is None) != (k_norm is None):
+            raise ValueError("attention: the norm over the projections comes with its eps and both weights")
+        if proj_norm_eps is not None and qk_norm_eps is not None:
+            raise ValueError("attention: a norm over the whole projections and a norm of every head exclude each other")
+        if score_bias is not None and (sinks is not None or qk_norm_eps is not None or gate is not None or proj_norm_eps is not None):
             raise ValueError("attention: sigmoid weights come without sinks, head norms or an output gate")
         if score_bias is not None and score_bias.numel() != n_heads:
             raise ValueError(f"attention: {score_bias.numel()} score biases for {n_heads} heads")
         self.score_bias = score_bias.to(torch.float32).contiguous() if score_bias is not None else None
-        self.extended = qk_norm_eps is not None or sinks is not None or gate is not None or (value_dim != head_dim and score_bias is None)
+        self.extended = (qk_norm_eps is not None or sinks is not None or gate is not None or proj_norm_eps is not None
+                         or (value_dim != head_dim and score_bias is None))
         if self.extended:
             self._init_extended(hidden_size, n_heads, n_kv_heads, head_dim, value_dim, score_scale, softcap, window, position,
                                 wq, wk, wv, wo, qk_norm_eps, sinks, gate, wg)
+            self.proj_norm = None
+            if proj_norm_eps is not None:
+                if q_norm.numel() != n_heads * head_dim or k_norm.numel() != n_kv_heads * head_dim:
+                    raise ValueError(f"attention: the projections' norms need {n_heads * head_dim} and {n_kv_heads * head_dim} weights")
+                D = self.head_dim
+
+                def columns(w, n):       # float32, laid out like the heads (zeros under their padding)
+                    out = torch.zeros((n, D), dtype=torch.float32, device=w.device)
+                    out[:, :head_dim] = w.to(torch.float32).view(n, head_dim)
+                    return out.view(n * D).contiguous()
+
+                self.proj_norm = (columns(q_norm, n_heads), columns(k_norm, n_kv_heads), float(proj_norm_eps),
+                                  n_heads * head_dim, n_kv_heads * head_dim)
             return
         if (wk is None) != (wv is None):
             raise ValueError("attention: keys and values come together or not at all")
@@ -128,8 +149,15 @@ class Attention:
         self.takes_deferred_rows = False      # the rows are rotated and normed in place: a tensor is needed
         self.delivers_branch = False
 
+    def _prepare_rows(self, rows, nh, nkv, hd, pages, prep):
+        """Norm, rotation and cache write of a step's packed rows, in one pass."""
+        if self.proj_norm is None:
+            return ops.rope_norm_cache(rows, nh, nkv, hd, pages=pages, norm_eps=self.qk_norm_eps, norm_dim=self.true_head_dim, **prep)
+        wq, wk, eps, q_count, k_count = self.proj_norm
+        return ops.rope_projnorm_cache(rows, nh, nkv, hd, pages=pages, wq=wq, wk=wk, eps=eps, q_count=q_count, k_count=k_count, **prep)
+
     def _forward_extended(self, x, batch, cache: RunCache):
-        """q, k, v and the gate in one product; rotation, head norm and cache write in one pass; attention with the
+        """q, k, v and the gate in one product; the norms, rotation and cache write in one pass; attention with the
         sinks; the gate; the output product."""
         if not cache.owns_kv:
             raise ValueError("attention: a run with head norms, sinks or an output gate keeps keys and values of its own")
@@ -143,18 +171,17 @@ class Attention:
         if self.position is not None and tables is None:
             raise ValueError("attention: with head norms the position part must offer tables()")
         prep = dict(tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, cos=tables[0] if tables else None,
-                    sin=tables[1] if tables else None, rotary_dim=rotary_dim, norm_eps=self.qk_norm_eps,
-                    norm_dim=self.true_head_dim, seq_end=batch.seq_end)
+                    sin=tables[1] if tables else None, rotary_dim=rotary_dim, seq_end=batch.seq_end)
         rows = ops.linear(x, self.w_qkv)
         if batch.is_decode:
-            ops.rope_norm_cache(rows, nh, nkv, hd, pages=pages, **prep)
+            self._prepare_rows(rows, nh, nkv, hd, pages, prep)
             ab = batch.attention_batch("all", self.window)
             ctx = ops.attention(rows, ab, pages, kind="decode" if fast_decode else "plain",
                                 scratch=lambda n: batch.scratch_buffer("decode", n), **common)
         else:
             # in a ring the write may overwrite rows of earlier steps that this step's early queries still need
             write_first = pages is not None and (not cache.is_ring or not batch.has_past)
-            ops.rope_norm_cache(rows, nh, nkv, hd, pages=pages if write_first else None, **prep)
+            self._prepare_rows(rows, nh, nkv, hd, pages if write_first else None, prep)
             ab = batch.attention_batch("past", self.window)
             if fast and batch.n_tiles:
                 kind = "prefill_tc" if (hd % 64 == 0 and not batch.has_past) else "prefill"
@@ -301,7 +328,9 @@ def _build_attention(spec: PartSpec, ctx: BuildContext) -> Attention:
                      score_bias=ctx.tensor(t["score_bias"]) if "score_bias" in t else None, cache_window=p.get("cache_window"),
                      value_dim=p.get("value_dim"), qk_norm_eps=p.get("qk_norm_eps"),
                      sinks=ctx.tensor(t["sinks"]) if "sinks" in t else None, gate=p.get("gate"),
-                     wg=ctx.tensor(t["g"]) if "g" in t else None)
+                     wg=ctx.tensor(t["g"]) if "g" in t else None, proj_norm_eps=p.get("proj_norm_eps"),
+                     q_norm=ctx.tensor(t["q_norm"]) if "q_norm" in t else None,
+                     k_norm=ctx.tensor(t["k_norm"]) if "k_norm" in t else None)
 
 
 register_part("mixer", "attention", _build_attention, replace=True)

@@ -20,7 +20,11 @@ Two ways of computing the same thing (`csrc/latent.cu`):
   * absorbed - single tokens, prompts that continue a cached sequence, and the 32-bit path:
     q'[h] = [W_uk[h]^T q_un[h] | q_rot[h]] attends over the cached rows as keys and as values with one
     key/value head; head h's output is W_uv[h] applied to the first kv_rank values of the result.
-Every size, the score scale, the window and the position encoding are parameters.
+Every size, the score scale, the window and the position encoding are parameters.  Two more, for designs that have them:
+  sinks           a learned logit per head without key or value: exp(sink_h) joins the softmax's denominator once, unscaled
+                  (tensor role "sinks")
+  gate_per_value  the output gate has a row of W_g for every value of every head, out = W_o (concat_h(o_h) * sigmoid(W_g h)),
+                  instead of one per head
 """
 from __future__ import annotations
 
@@ -51,11 +55,18 @@ class LatentAttention:
     delivers_branch = True         # the output projection may deliver the result through a stream's sink
 
     def __init__(self, *, hidden_size, n_heads, dim, rot_dim, vdim, kv_rank, score_scale, window, cache_window, eps,
-                 position, wq, wdkv, dkv_norm, wuk, wuv, wg, wo):
+                 position, wq, wdkv, dkv_norm, wuk, wuv, wg, wo, sinks=None, gate_per_value=False):
         H, d, rd, vd, r = n_heads, dim, rot_dim, vdim, kv_rank
         self.hidden_size, self.n_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = hidden_size, H, d, rd, vd, r
         self.score_scale, self.window, self.cache_window, self.eps = float(score_scale), window, cache_window, float(eps)
         self.position = position
+        self.gate_per_value = bool(gate_per_value)
+        self.gate_width = H * vd if self.gate_per_value else H
+        if wg.shape[0] != self.gate_width:
+            raise ValueError(f"latent attention: the gate's matrix has {wg.shape[0]} rows, {self.gate_width} are needed")
+        if sinks is not None and sinks.numel() != H:
+            raise ValueError(f"latent attention: {sinks.numel()} sinks for {H} heads")
+        self.sinks = sinks.to(torch.float32).contiguous() if sinks is not None else None
         if not (hasattr(position, "tables") and hasattr(position, "rotary_dim")) or position.rotary_dim > rd:
             raise ValueError("latent attention needs a position encoding with tables over at most rot_dim dimensions")
         self.owns_latent = wdkv is not None
@@ -95,7 +106,8 @@ class LatentAttention:
                     norm=self.latent_norm, cos=cos, sin=sin, rot_n=self.position.rotary_dim,
                     interleaved=getattr(self.position, "interleaved", False), tok_seq=batch.tok_seq, tok_pos=batch.tok_pos,
                     pages=pages, seq_end=batch.seq_end)
-        gate = rows[:, self.gate_col:self.gate_col + H]
+        gate = rows[:, self.gate_col:self.gate_col + self.gate_width]
+        per_value = self.gate_per_value
         bf16 = rows.dtype is torch.bfloat16
         owner_rows = None if cache.owns_kv else batch.new_kv.get(cache_owner(batch, run))
         whole_prompts = not batch.is_decode and not batch.has_past and (cache.owns_kv or owner_rows is not None)
@@ -113,8 +125,8 @@ class LatentAttention:
             ab = batch.attention_batch("past", self.window)
             ctx = ops.attention(packed, ab, None, n_heads=H, n_kv_heads=H, head_dim=self.pad, score_scale=self.score_scale,
                                 softcap=None, window=self.window, new_kv=(packed, H * self.pad, 2 * H * self.pad),
-                                kind="prefill_tc" if self.pad % 64 == 0 else "prefill", status=batch.status)
-            return ops.linear_branch(ops.gate_heads(ctx, self.pad, gate, H, vd), self.w_o, sink)
+                                kind="prefill_tc" if self.pad % 64 == 0 else "prefill", status=batch.status, sinks=self.sinks)
+            return ops.linear_branch(ops.gate_heads(ctx, self.pad, gate, H, vd, per_value=per_value), self.w_o, sink)
 
         # ---- absorbed ----
         qp = torch.empty((rows.shape[0], H * width), dtype=rows.dtype, device=rows.device)
@@ -131,7 +143,8 @@ class LatentAttention:
             qp.view(T, H, width)[:, :, :r].copy_(torch.bmm(q_un, self.w_uk_b).transpose(0, 1))
         else:
             ops.heads_linear(rows, 0, d + rd, self.w_uk_t, out=qp, out_col=0, out_head=width)
-        common = dict(n_heads=H, n_kv_heads=1, head_dim=width, score_scale=self.score_scale, softcap=None, window=self.window)
+        common = dict(n_heads=H, n_kv_heads=1, head_dim=width, score_scale=self.score_scale, softcap=None, window=self.window,
+                      sinks=self.sinks)
         if batch.is_decode or (not cache.owns_kv and owner_rows is None):
             ab = batch.attention_batch("all", self.window)
             generic = bf16 and batch.is_decode and H <= 8 and width % 16 == 0 and width <= 256 \
@@ -139,7 +152,7 @@ class LatentAttention:
             if batch.is_decode and LATENT_DECODE == "own" and ops.latent_decode_ok(rows.dtype, width, r, cache.page_size):
                 # all heads of a token share the cached rows a block has brought in
                 ctx = ops.latent_decode(qp, ab, pages, n_heads=H, kv_rank=r, score_scale=self.score_scale, window=self.window,
-                                        scratch=lambda n: batch.scratch_buffer("latent_decode", n))
+                                        scratch=lambda n: batch.scratch_buffer("latent_decode", n), sinks=self.sinks)
             else:
                 ctx = ops.attention(qp, ab, pages, kind="decode" if generic else "plain",
                                     scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
@@ -160,9 +173,9 @@ class LatentAttention:
                     write()
         if batched:
             per_head = torch.bmm(ctx.as_strided((H, T, r), (width, ctx.stride(0), 1)), self.w_uv_h.transpose(1, 2))     # [H, T, vdim]
-            o = ops.gate_heads(per_head, T * vd, gate, H, vd, row_stride=vd, n_rows=T)
+            o = ops.gate_heads(per_head, T * vd, gate, H, vd, row_stride=vd, n_rows=T, per_value=per_value)
         else:
-            o = ops.heads_linear(ctx, 0, width, self.w_uv_h, gate=gate)
+            o = ops.heads_linear(ctx, 0, width, self.w_uv_h, gate=gate, gate_per_value=per_value)
         return ops.linear_branch(o, self.w_o, sink)
 
 
@@ -174,7 +187,7 @@ def _build_latent_attention(spec: PartSpec, ctx: BuildContext) -> LatentAttentio
                            kv_rank=p["kv_rank"], score_scale=p["score_scale"], window=p.get("window"),
                            cache_window=p.get("cache_window", p.get("window")), eps=p["eps"], position=position,
                            wq=get("q"), wdkv=get("dkv"), dkv_norm=get("dkv_norm"), wuk=get("uk"), wuv=get("uv"), wg=get("g"),
-                           wo=get("o"))
+                           wo=get("o"), sinks=get("sinks"), gate_per_value=p.get("gate_per_value", False))
 
 
 register_part("mixer", "latent_attention", _build_latent_attention, replace=True)

@@ -44,10 +44,17 @@ register_part("embedding", "scaled_embedding",
 
 
 class LinearHead:
-    """float32 logits = soft-cap(n W^T) * scale (the scale applied to the float32 result, after any soft-cap)."""
+    """float32 logits = soft-cap(pre_scale * n W^T) * scale: `pre_scale` multiplies the products before any soft-cap,
+    `scale` the float32 result after it.  cap tanh(p z / cap) = p (cap / p) tanh(z / (cap / p)), so a pre_scale p runs as a
+    soft-cap of cap / p in the product's epilogue followed by the scale p (times `scale`)."""
 
-    def __init__(self, weight: torch.Tensor, softcap: Optional[float], scale: float = 1.0):
-        self.weight, self.softcap, self.scale = weight, softcap, float(scale)
+    def __init__(self, weight: torch.Tensor, softcap: Optional[float], scale: float = 1.0, pre_scale: float = 1.0):
+        pre_scale = float(pre_scale)
+        if pre_scale <= 0.0:
+            raise ValueError(f"linear_head: pre_scale must be positive, got {pre_scale}")
+        self.weight = weight
+        self.softcap = float(softcap) / pre_scale if softcap is not None else None
+        self.scale = float(scale) * pre_scale
 
     takes_deferred_rows = True      # n goes into one product and nowhere else
 
@@ -58,7 +65,7 @@ class LinearHead:
 
 register_part("head", "linear_head",
               lambda spec, ctx: LinearHead(ctx.tensor(spec.tensors["weight"]), spec.params.get("softcap"),
-                                           spec.params.get("scale", 1.0)),
+                                           spec.params.get("scale", 1.0), spec.params.get("pre_scale", 1.0)),
               replace=True)
 
 
@@ -156,12 +163,17 @@ class ParallelBlock:
                        last n is state the block keeps per slot, beside the mixer's own (`needs()`); tensor role "shift".
       gated_residual   c1 = sigmoid(R1 n + b1), c2 = sigmoid(R2 n + b2), element by element (c = 1 without it); tensor
                        roles "gate_mixer", "gate_mixer_bias", "gate_ff", "gate_ff_bias".  Both gates are one product.
+      branch_scale     x <- x + s * (mixer(n) + ff(n)) with a constant s (1 without it; not together with gated_residual).
     The norm, the shift, the gates' sigmoids and the sum run in float32 on the stream (one kernel before the sublayers,
     one after).  A feed-forward that keeps parts of its result apart (`forward_parts`) has them added in that last kernel.
-    A layer without a feed-forward has the mixer's branch only."""
+    A layer without a feed-forward has the mixer's branch only.  Without shift and gates the block leaves its sum to
+    the stream (`ResidualStream.add_sum`), which forms it together with the norm the next part asks for, in one kernel."""
 
-    def __init__(self, mixer, feed_forward, norm, act_dtype: torch.dtype, hidden_size: int, shift, gates):
+    def __init__(self, mixer, feed_forward, norm, act_dtype: torch.dtype, hidden_size: int, shift, gates, branch_scale: float = 1.0):
         self.mixer, self.feed_forward, self.norm, self.act_dtype, self.hidden_size = mixer, feed_forward, norm, act_dtype, hidden_size
+        self.branch_scale = float(branch_scale)
+        if gates is not None and self.branch_scale != 1.0:
+            raise ValueError("parallel block: a constant on the branches and gates on them exclude each other")
         if not callable(getattr(norm, "fused_params", None)) or norm.fused_params().offset != 0.0:
             raise ValueError("parallel block: the norm must be a scale-only root-mean-square norm without an offset")
         self.shift = shift
@@ -188,8 +200,21 @@ class ParallelBlock:
         rest = cache.state[1 if self.shift is not None else 0:]
         return cache._replace(state=rest if isinstance(self._mixer_state, (tuple, list)) else rest[0])
 
+    def _feed_forward_parts(self, n):
+        if self.feed_forward is None:
+            return None, None
+        if hasattr(self.feed_forward, "forward_parts"):
+            return self.feed_forward.forward_parts(n)
+        return self.feed_forward.forward(n), None
+
     def forward(self, stream: ResidualStream, batch, cache, run: int):
         stream.norm_after_block = None
+        if self.shift is None and self.w_gates is None:
+            n = stream.normed(self.norm, self.act_dtype)
+            a = self.mixer.forward(n, batch, self._mixer_cache(cache), run)
+            f1, f2 = self._feed_forward_parts(n)
+            stream.add_sum((a, f1, f2), self.branch_scale)
+            return
         x = stream.writable()
         p = self.norm.fused_params()
         if self.shift is not None:
@@ -198,18 +223,11 @@ class ParallelBlock:
         else:
             n = m = self.norm.apply(x, self.act_dtype)
         a = self.mixer.forward(m, batch, self._mixer_cache(cache), run)
-        f1 = f2 = None
-        if self.feed_forward is not None:
-            if hasattr(self.feed_forward, "forward_parts"):
-                f1, f2 = self.feed_forward.forward_parts(n)
-            else:
-                f1 = self.feed_forward.forward(n)
+        f1, f2 = self._feed_forward_parts(n)
         if self.w_gates is not None:
             ops.gated_residual_add_(x, ops.linear(n, self.w_gates), self.b_mixer, a, self.b_ff, f1, f2)
         else:
-            for branch in (a, f1, f2):
-                if branch is not None:
-                    ops.residual_add_(x, branch)
+            ops.add_branches_norm_(x, (a, f1, f2), self.branch_scale)
 
 
 def _build_parallel(layer: LayerSpec, ctx: BuildContext) -> ParallelBlock:
@@ -222,7 +240,7 @@ def _build_parallel(layer: LayerSpec, ctx: BuildContext) -> ParallelBlock:
     if layer.params.get("gated_residual"):
         gates = (ctx.tensor(t["gate_mixer"]), ctx.tensor(t["gate_mixer_bias"]),
                  ctx.tensor(t["gate_ff"]) if ff is not None else None, ctx.tensor(t["gate_ff_bias"]) if ff is not None else None)
-    return ParallelBlock(mixer, ff, norm, ctx.dtype, layer.params["hidden_size"], shift, gates)
+    return ParallelBlock(mixer, ff, norm, ctx.dtype, layer.params["hidden_size"], shift, gates, layer.params.get("branch_scale", 1.0))
 
 
 register_part("block", "parallel", _build_parallel, replace=True)

@@ -13,6 +13,9 @@ the branch, add it to the stream, norm the sum for the next part" is ONE kernel
 that reads the branch and the stream once.  Any other norm kind (anything with an
 `apply`) takes the same route through separate kernels.
 
+For blocks whose sublayers all read ONE norm the stream offers `add_sum(branches, scale)`: x <- x + scale * (sum of the
+branches), formed in float32 together with the norm the next part asks for (`ops.add_branches_norm_`, one kernel).
+
 For blocks that norm AFTER the sum the stream offers `rows(dtype)` (the stream itself as a part's input) and
 `renorm(branch, norm, alpha, dtype)`: x <- norm(alpha x + branch) in float32, in place, in one kernel that also
 leaves x in the activations' dtype for the next part.
@@ -81,6 +84,7 @@ class ResidualStream:
             raise ValueError("the residual stream is float32")
         self.x = x
         self._pending = None     # (branch: tensor or ops.Branch, post_norm or None)
+        self._pending_sum = None     # (branches, scale): x + scale * (sum of the branches), waiting for the next norm
         self._operand = None     # (bfloat16 [16, hidden] whose first rows are x times a norm's column factors, that norm)
         self._lent = None        # DeferredRows handed out; x is valid once they have been used
         self._rows = None        # x in the activations' dtype, as `renorm` left it (valid until x changes again)
@@ -137,7 +141,20 @@ class ResidualStream:
         self._rows = None
         self._pending = (branch, post_norm)
 
+    def add_sum(self, branches, scale: float = 1.0):
+        """x <- x + scale * (b0 + b1 + ...) for the (one to three, None skipped) branches of a block whose sublayers read
+        one norm; done lazily, so that the next `normed` forms the sum and its norm in one kernel."""
+        self._settled()
+        self._flush()
+        self._rows = None
+        self._pending_sum = (tuple(b for b in branches if b is not None), float(scale))
+
     def _flush(self):
+        if self._pending_sum is not None:
+            branches, scale = self._pending_sum
+            self._pending_sum = None
+            self._operand = None
+            ops.add_branches_norm_(self.x, branches, scale)
         if self._pending is None:
             return
         branch, post = self._pending
@@ -155,6 +172,12 @@ class ResidualStream:
         `ops.DeferredRows`.  upcoming: the norm the stream will be asked for after the next branch, if the
         caller knows it and both sides of that branch can use the split form."""
         self._settled()
+        if self._pending_sum is not None and _fusable(norm):
+            branches, scale = self._pending_sum
+            self._pending_sum = None
+            y = ops.add_branches_norm_(self.x, branches, scale, norm.fused_params(), out_dtype)
+            self._prepare(upcoming, out_dtype)
+            return y
         if self._pending is not None and isinstance(self._pending[0], ops.Branch):
             branch, post = self._pending
             if deferred_ok and out_dtype is branch.dtype and self._announced(branch, post, norm):

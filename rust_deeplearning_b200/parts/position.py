@@ -15,7 +15,11 @@ f_i / factor:
     lo, hi = max(floor(d(fast)), 0), min(ceil(d(slow)), n - 1)
     ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
     f_i   <- f_i / factor * ramp_i + f_i (1 - ramp_i)
-and multiplies cos and sin by 0.1 ln(factor) + 1.  Both are in the tables, so kernels need not know of them.
+and multiplies cos and sin by 0.1 ln(factor) + 1.  A second kind, {"kind": "llama3", "factor", "low", "high",
+"original"}, slows the long wavelengths down and leaves the short ones alone: with l_i = 2 pi / f_i,
+    l_i < original / high:  f_i stays;      l_i > original / low:  f_i <- f_i / factor;
+    between:  s = (original / l_i - low) / (high - low),   f_i <- (1 - s) f_i / factor + s f_i
+(cos and sin keep their size).  All of it is in the tables, so kernels need not know of it.
 
 Interface of a position encoding, as an attention mixer uses it:
 `rotate(rows, n_heads, n_kv_heads, head_dim, batch)` rotates, in place, the query and
@@ -42,8 +46,18 @@ def rotary_frequencies(theta: float, n: int, scaling: Optional[dict] = None):
     inv = torch.tensor(float(theta), dtype=torch.float64) ** (-2.0 * i / n)
     if scaling is None:
         return inv, 1.0
+    if scaling.get("kind") == "llama3":
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        low, high = float(scaling["low"]), float(scaling["high"])
+        if high == low:
+            raise ValueError("rotary scaling 'llama3': low and high must differ")
+        wavelength = 2.0 * math.pi / inv
+        s = (original / wavelength - low) / (high - low)
+        blended = (1.0 - s) * inv / factor + s * inv
+        out = torch.where(wavelength < original / high, inv, torch.where(wavelength > original / low, inv / factor, blended))
+        return out, 1.0
     if scaling.get("kind") != "yarn":
-        raise ValueError(f"rotary scaling of kind {scaling.get('kind')!r} is not known (known: 'yarn')")
+        raise ValueError(f"rotary scaling of kind {scaling.get('kind')!r} is not known (known: 'yarn', 'llama3')")
     factor, original = float(scaling["factor"]), float(scaling["original"])
     d = lambda turns: n * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
     lo = max(math.floor(d(float(scaling["fast"]))), 0)

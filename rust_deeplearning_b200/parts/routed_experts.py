@@ -11,7 +11,9 @@ output is x itself.  Rows are independent of each other, so packing and batching
 Interface: `forward(x [rows, hidden] normed) -> [rows, hidden]`.
 
 Further parameters, for designs that have them:
-  scoring           "softmax" (above) or "sigmoid": s = sigmoid(z), every expert's score by itself
+  scoring           "softmax" (above), "sigmoid": s = sigmoid(z), every expert's score by itself, or "softmax_chosen": the
+                    `top` largest logits are taken and their weights are the softmax over those logits alone
+  router_bias       a learned number per expert added to the logits, z = W_r x + b (tensor role "router_bias")
   form              a name of `ops.UNARY_FORMS` ("relu2", ...): experts of two matrices, W_down act(W_up x), built from
                     `up<e>` and `down<e>` alone
   weights_on_input  y = sum_k expert_{e_k}(s[e_k] * x): the score multiplies what the expert reads, not what it returns
@@ -29,7 +31,7 @@ from .spec import PartSpec
 
 class RoutedExperts:
     def __init__(self, *, hidden_size, expert_size, n_experts, n_identity, top, form, form_param, w_router, correction,
-                 gates, ups, downs, scoring="softmax", weights_on_input=False, shared=None):
+                 gates, ups, downs, scoring="softmax", weights_on_input=False, shared=None, router_bias=None):
         if form not in ops.EXPERT_FORMS:
             raise ValueError(f"routed_experts: unknown expert form '{form}', known: {sorted(ops.EXPERT_FORMS)}")
         if scoring not in ops.ROUTE_SCORING:
@@ -42,6 +44,7 @@ class RoutedExperts:
         self.scoring, self.weights_on_input = scoring, bool(weights_on_input)
         self.w_router = w_router.to(torch.float32).contiguous()
         self.correction = correction.to(torch.float32).contiguous() if correction is not None else None
+        self.router_bias = router_bias.to(torch.float32).contiguous() if router_bias is not None else None
         # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows ([experts, ff, hidden] for experts of two
         # matrices); [experts, hidden, ff]
         if not n_experts:
@@ -60,7 +63,7 @@ class RoutedExperts:
 
     def forward_parts(self, x):
         """(the routed experts' sum, the shared expert's result or None), each [rows, hidden]."""
-        sel, sel_w = ops.moe_route(x, self.w_router, self.correction, self.top, self.scoring)
+        sel, sel_w = ops.moe_route(x, self.w_router, self.correction, self.top, self.scoring, bias=self.router_bias)
         routed = ops.moe_experts(x, sel, sel_w, self.w_gate_up, self.w_down, self.n_experts, self.form, self.form_param,
                                  weights_on_input=self.weights_on_input)
         if self.shared is None:
@@ -94,7 +97,8 @@ def _build_routed_experts(spec: PartSpec, ctx: BuildContext) -> RoutedExperts:
                          w_router=ctx.tensor(t["router"]), correction=ctx.tensor(t["correction"]) if "correction" in t else None,
                          gates=[] if unary else [ctx.tensor(t[f"gate{e}"]) for e in range(E)],
                          ups=[ctx.tensor(t[f"up{e}"]) for e in range(E)], downs=[ctx.tensor(t[f"down{e}"]) for e in range(E)],
-                         scoring=p.get("scoring", "softmax"), weights_on_input=p.get("weights_on_input", False), shared=shared)
+                         scoring=p.get("scoring", "softmax"), weights_on_input=p.get("weights_on_input", False), shared=shared,
+                         router_bias=ctx.tensor(t["router_bias"]) if "router_bias" in t else None)
 
 
 register_part("feed_forward", "routed_experts", _build_routed_experts, replace=True)
