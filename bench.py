@@ -291,6 +291,21 @@ def revepel_shape(width, ssm_heads, state, heads, kv_heads, dim, window, experts
             "max_positions": CONTEXT, "layers": out}
 
 
+def gasetar_shape(width, heads, kv_heads, dim, window, latent_heads, latent_dim, rot_dim, vdim, kv_rank, experts, top, ff, shared_ff,
+                  dense_ff, vocab, layers=4):
+    """A Gasetar configuration of four layers: window attention with a dense feed-forward, latent attention with routed
+    experts, and two window-attention layers with routed experts (each with a shared expert)."""
+    rot = {"base": 50000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "mask": {"size": window}, "rot": rot}
+    latent = {"heads": latent_heads, "dim": latent_dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+              "scale": (latent_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+    order = [("attention", attn, {"kind": "dense", "ff": dense_ff}), ("latent_attention", latent, moe), ("attention", attn, moe), ("attention", attn, moe)]
+    return {"architecture": "Gasetar", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "residual_mult": 0.5, "logit_scale": 1.0, "logit_softcap": 30.0, "max_positions": CONTEXT,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in order[:layers]]}
+
+
 DESIGN_SIZES = {
     # name: (the design's arguments, the Gemma 2 arguments of equal width / heads / active feed-forward width)
     "w1024": (dict(width=1024, heads=8, dim=64, rot_dim=64, vdim=128, kv_rank=192, window=1024, experts=16, identity=2, top=2, ff=1024,
@@ -319,10 +334,22 @@ REVEPEL_SIZES = {
                    shared_ff=4096, layers=4, vocab=32000),
               dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, layers=4, vocab=32000)),
 }
+GASETAR_SIZES = {
+    # four layers each (window attention + dense, latent attention + experts, two of window attention + experts); Gemma 2 with
+    # the same width, heads, key heads, head size and window, and a feed-forward as wide as the experts a token uses (top x ff + shared)
+    "w1024": (dict(width=1024, heads=8, kv_heads=4, dim=128, window=1024, latent_heads=8, latent_dim=64, rot_dim=64, vdim=128, kv_rank=192,
+                   experts=16, top=2, ff=768, shared_ff=512, dense_ff=2048, vocab=32000),
+              dict(width=1024, heads=8, kv_heads=4, head_dim=128, intermediate=2048, window=1024, layers=4, vocab=32000)),
+    "w2048": (dict(width=2048, heads=16, kv_heads=8, dim=128, window=4096, latent_heads=16, latent_dim=128, rot_dim=64, vdim=128, kv_rank=512,
+                   experts=64, top=6, ff=1024, shared_ff=2304, dense_ff=8448, vocab=32000),
+              dict(width=2048, heads=16, kv_heads=8, head_dim=128, intermediate=8448, window=4096, layers=4, vocab=32000)),
+}
 # design -> (its shape, its sizes, the title, the registered design it stands beside and that design's shape)
 DESIGNS = {"ligirax": (ligirax_shape, DESIGN_SIZES, "ligirax beside gemma2 at equal width, heads and active feed-forward width", "gemma2", gemma_like),
            "dokulorn": (dokulorn_shape, DOKULORN_SIZES, "dokulorn beside gemma2 at equal width, heads, head size and feed-forward width", "gemma2",
                         gemma_like),
+           "gasetar": (gasetar_shape, GASETAR_SIZES, "gasetar beside gemma2 at equal width, heads, key heads, head size, window and active feed-forward width",
+                       "gemma2", gemma_like),
            "revepel": (revepel_shape, REVEPEL_SIZES, "revepel beside dokulorn at equal width, heads, head size and active feed-forward width",
                        "dokulorn", dokulorn_shape)}
 
@@ -415,7 +442,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
     ap.add_argument("--context", type=int, default=PROMPT, help="prompt length of the --only decode case")
     ap.add_argument("--no-large", action="store_true", help="leave out the 9B and 27B shapes and the long contexts")
-    ap.add_argument("--design", choices=["ligirax", "dokulorn", "revepel"], default=None,
+    ap.add_argument("--design", choices=["ligirax", "dokulorn", "revepel", "gasetar"], default=None,
                     help="instead of the default workload: prefill and decode of this design beside its closest registered design "
                          "(Gemma 2; for revepel, Dokulorn) at equal layer sizes")
     ap.add_argument("--size", default=None, help="with --design: one of the sizes only")

@@ -100,9 +100,10 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(LatentPrepar
     for (int i = threadIdx.x; i < width; i += LP_THREADS) dst[rdl_cache_col<T>(r, i, width)] = out[i];
 }
 
-// The same work in bfloat16 with 16-byte accesses, for interleaved pairs where every size and offset is a whole number of
-// 8-value chunks: a chunk of the rotated parts holds four whole pairs, a chunk of the latent goes to the rows and to its
-// (swizzled) place in the cache as soon as it is normed.  The sum of squares is formed chunk by chunk, then by the block's
+// The same work in bfloat16 with 16-byte accesses, where every size and offset is a whole number of 8-value chunks: with
+// interleaved pairs a chunk of the rotated parts holds four whole pairs; with half-split pairs (rot_n a multiple of 16)
+// chunk c of the first half turns together with chunk c + rot_n / 16 of the second.  A chunk of the latent goes to the
+// rows and to its (swizzled) place in the cache as soon as it is normed.  The sum of squares is formed chunk by chunk, then by the block's
 // fixed tree: its order depends on kv_rank alone.
 __device__ __forceinline__ uint4 rotate_chunk(const uint4 raw, const float* __restrict__ cs, const float* __restrict__ sn) {
     const float4 c4 = *reinterpret_cast<const float4*>(cs), s4 = *reinterpret_cast<const float4*>(sn);
@@ -118,6 +119,21 @@ __device__ __forceinline__ uint4 rotate_chunk(const uint4 raw, const float* __re
     return out;
 }
 
+// half-split pairs: value i of chunk `lo` turns with value i of chunk `hi` by the eight angles at cs, sn
+__device__ __forceinline__ void rotate_half_chunks(uint4& lo, uint4& hi, const float* __restrict__ cs, const float* __restrict__ sn) {
+    const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat162* u = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(u[i]), y = __bfloat1622float2(v[i]);
+        u[i] = __floats2bfloat162_rn(x.x * c[2 * i] - y.x * s[2 * i], x.y * c[2 * i + 1] - y.y * s[2 * i + 1]);
+        v[i] = __floats2bfloat162_rn(y.x * c[2 * i] + x.x * s[2 * i], y.y * c[2 * i + 1] + x.y * s[2 * i + 1]);
+    }
+}
+
 __global__ void __launch_bounds__(LP_THREADS) latent_prepare_vec_kernel(LatentPrepareArgs a) {
     __shared__ float red[33];
     rdl_grid_wait();
@@ -131,14 +147,24 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_vec_kernel(LatentPr
     const float* cs = a.cos_t + (long long)pos * half;
     const float* sn = a.sin_t + (long long)pos * half;
     const int hq = a.dim + a.rot_dim, rc = a.rot_dim >> 3, rot_chunks = a.rot_n >> 3;
-    // queries: chunk c of head h's rotated part
-    for (int idx = threadIdx.x; idx < a.n_heads * rc; idx += LP_THREADS) {
-        const int h = idx / rc, c = idx - h * rc;
+    const int hcn = a.interleaved ? 0 : rot_chunks >> 1;      // half-split pairs: chunk c turns with chunk c + hcn
+    // queries: chunk c of head h's rotated part (half-split pairs: a work item holds both chunks of a pair)
+    const int q_items = rc - hcn;
+    for (int idx = threadIdx.x; idx < a.n_heads * q_items; idx += LP_THREADS) {
+        const int h = idx / q_items, j = idx - h * q_items;
+        const int c = j < hcn ? j : j + hcn;
         T* src = row + a.q_col + (long long)h * hq + a.dim + c * 8;
         T* dst = a.q_rot_out ? (T*)a.q_rot_out + (long long)t * a.q_rot_stride + (long long)h * a.q_rot_head + c * 8 : src;
         uint4 v = *reinterpret_cast<const uint4*>(src);
-        if (c < rot_chunks) v = rotate_chunk(v, cs + c * 4, sn + c * 4);
-        else if (dst == src) continue;
+        if (j < hcn) {
+            uint4 w = *reinterpret_cast<const uint4*>(src + hcn * 8);
+            rotate_half_chunks(v, w, cs + c * 8, sn + c * 8);
+            *reinterpret_cast<uint4*>(dst + hcn * 8) = w;
+        } else if (a.interleaved && c < rot_chunks) {
+            v = rotate_chunk(v, cs + c * 4, sn + c * 4);
+        } else if (dst == src) {
+            continue;
+        }
         *reinterpret_cast<uint4*>(dst) = v;
     }
     if (a.latent_col < 0) return;              // a layer that reads another layer's latent rows
@@ -181,8 +207,15 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_vec_kernel(LatentPr
                                              x.y * inv * rdl_load(a.norm_w, c * 8 + 2 * i + 1, a.norm_w_dtype));
             }
             v = res;
-        } else if (c - lc < rot_chunks) {
+        } else if (a.interleaved && c - lc < rot_chunks) {
             v = rotate_chunk(v, cs + (c - lc) * 4, sn + (c - lc) * 4);
+        } else if (c - lc < hcn) {             // half-split pairs: this chunk and its partner, both stored here
+            uint4 w = *reinterpret_cast<const uint4*>(lat + (c + hcn) * 8);
+            rotate_half_chunks(v, w, cs + (c - lc) * 8, sn + (c - lc) * 8);
+            *reinterpret_cast<uint4*>(out + (c + hcn) * 8) = w;
+            if (cache_row) *reinterpret_cast<uint4*>(cache_row + rdl_swizzled_chunk(r, c + hcn, chunks) * 8) = w;
+        } else if (c - lc < 2 * hcn) {
+            continue;                          // stored by its partner's thread
         }
         *reinterpret_cast<uint4*>(out + c * 8) = v;
         if (cache_row) *reinterpret_cast<uint4*>(cache_row + rdl_swizzled_chunk(r, c, chunks) * 8) = v;
@@ -393,7 +426,7 @@ extern "C" int rdl_latent_prepare(const LatentPrepareArgs* a, void* stream) {
                                  a->ring_pages <= a->table_width), "latent_prepare: cache write without storage or with bad paging");
     if (a->n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const bool chunked = a->dtype == RDL_BF16 && a->interleaved && a->rot_n % 8 == 0 && a->dim % 8 == 0 && a->rot_dim % 8 == 0 && a->kv_rank % 8 == 0 &&
+    const bool chunked = a->dtype == RDL_BF16 && a->rot_n % (a->interleaved ? 8 : 16) == 0 && a->dim % 8 == 0 && a->rot_dim % 8 == 0 && a->kv_rank % 8 == 0 &&
                          a->q_col % 8 == 0 && a->row_stride % 8 == 0 && ((uintptr_t)a->rows & 15) == 0 && (a->latent_col < 0 || a->latent_col % 8 == 0) &&
                          (!a->q_rot_out || (((uintptr_t)a->q_rot_out & 15) == 0 && a->q_rot_stride % 8 == 0 && a->q_rot_head % 8 == 0)) &&
                          (a->latent_col < 0 || ((uintptr_t)a->latent_out & 15) == 0) && (!a->do_write || ((uintptr_t)a->cache & 15) == 0) &&

@@ -137,14 +137,15 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
                                                                    const float* __restrict__ correction, int n_rows,
                                                                    int n_experts, int top, int scoring, int* __restrict__ sel,
                                                                    float* __restrict__ sel_w) {
-    extern __shared__ float zs_all[];          // per warp: [n_experts] scores, [n_experts] choices
+    extern __shared__ float zs_all[];          // per warp: [n_experts] scores, [n_experts] choices, [top] chosen scores
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * TOPK_WARPS + warp;
     if (t >= n_rows) return;
-    float* zs = zs_all + (size_t)warp * 2 * n_experts;
+    float* zs = zs_all + (size_t)warp * (2 * n_experts + top);
     float* choice = zs + n_experts;
+    float* picked = choice + n_experts;
     const float* zr = z + (long long)t * n_experts;
     float m = -INFINITY;
     float sum = 1.f;
@@ -187,18 +188,18 @@ __global__ void __launch_bounds__(TOPK_WARPS * 32) moe_topk_kernel(const float* 
         if (best_e == 0x7fffffff) best_e = 0;              // only if every remaining choice is NaN or -inf
         if (lane == 0) {
             sel[(long long)t * top + k] = best_e;
-            sel_w[(long long)t * top + k] = zs[best_e];
+            if (scoring == RDL_ROUTE_SOFTMAX_CHOSEN) picked[k] = zs[best_e];
+            else sel_w[(long long)t * top + k] = zs[best_e];
             choice[best_e] = -INFINITY;
         }
         __syncwarp();
     }
     if (scoring == RDL_ROUTE_SOFTMAX_CHOSEN && lane == 0) {
         // the weights: a softmax over the chosen logits alone (the first chosen is the largest), summed in the order of the choice
-        float* w = sel_w + (long long)t * top;
-        const float top_logit = w[0];
+        const float top_logit = picked[0];
         float total = 0.f;
-        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - top_logit); total += w[k]; }
-        for (int k = 0; k < top; ++k) w[k] /= total;
+        for (int k = 0; k < top; ++k) { picked[k] = expf(picked[k] - top_logit); total += picked[k]; }
+        for (int k = 0; k < top; ++k) sel_w[(long long)t * top + k] = picked[k] / total;
     }
 }
 
@@ -473,7 +474,7 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
         if (few) RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float, ROUTE_FEW_ROWS, true>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
         else RDL_CHECK_EX(rdl_launch(moe_logits_kernel<float, ROUTE_MANY_ROWS, false>, grid, block, 0, st, xp, w_router, n_rows, n_experts, width, logits), "moe_route");
     }
-    const size_t smem = (size_t)TOPK_WARPS * 2 * n_experts * sizeof(float);
+    const size_t smem = (size_t)TOPK_WARPS * (2 * n_experts + top) * sizeof(float);
     RDL_CHECK_EX(rdl_launch(moe_topk_kernel, dim3((n_rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(TOPK_WARPS * 32), smem, st, (const float*)logits,
                             bias, correction, n_rows, n_experts, top, scoring, sel, sel_w), "moe_route");
     return 0;

@@ -392,7 +392,11 @@ __global__ void __launch_bounds__(256) rope_norm_cache_vec_kernel(T* __restrict_
 // One block per token.  First the two sums of squares (lane by lane, across each warp, then the warps' parts in rising
 // order: the order depends on the sizes alone), then a work item per rotated pair of pieces, per piece that does not
 // rotate and per value piece; all in float, every value rounded once on the way back into the row and into the cache.
-// VEC: pieces of 16 bytes (head_dim and rotary_dim / 2 whole numbers of them), else single values.
+// VEC: pieces of 16 bytes (head_dim and rotary_dim / 2 whole numbers of them; weights and angles then come four at a time),
+// else single values.
+// Two other forms were measured on 2,048 tokens of 16 + 8 heads of 128 and not kept (this one, 256 threads: 23.4 us): a block
+// per token with its pieces held in registers across the sums, 32.4 us, and a warp per token with its pieces in registers and
+// the sums by shuffles, 49.9 us (33 us for 8 tokens): their unrolled bodies are long straight-line code that every warp runs once.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) rope_projnorm_cache_kernel(T* __restrict__ rows, long long row_stride, int n_heads, int n_kv_heads,
                                                                   int head_dim, int rotary_dim, const float* __restrict__ cos_t,
@@ -419,6 +423,17 @@ __global__ void __launch_bounds__(256) rope_projnorm_cache_kernel(T* __restrict_
     auto store = [](T* p, const float (&f)[N]) {
         if constexpr (VEC) *reinterpret_cast<uint4*>(p) = Chunk<T>::pack(f);
         else *p = from_float<T>(f[0]);
+    };
+    auto table = [](const float* p, float (&f)[N]) {      // N weights or angles
+        if constexpr (VEC) {
+#pragma unroll
+            for (int e = 0; e < N; e += 4) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(p + e));
+                f[e] = v.x; f[e + 1] = v.y; f[e + 2] = v.z; f[e + 3] = v.w;
+            }
+        } else {
+            f[0] = *p;
+        }
     };
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x * N; i < qw + kw; i += blockDim.x * N) {
@@ -447,13 +462,13 @@ __global__ void __launch_bounds__(256) rope_projnorm_cache_kernel(T* __restrict_
     const int per_head = chunks - hc;                      // pairs, then pieces that do not rotate
     const int qk_items = (n_heads + n_kv_heads) * per_head;
     const int total = qk_items + (write ? n_kv_heads * chunks : 0);
-    const int* table = tables + (long long)seq * table_width;
+    const int* page_list = tables + (long long)seq * table_width;
     for (int it = threadIdx.x; it < total; it += blockDim.x) {
         if (it >= qk_items) {                              // a piece of a value head, copied as it is
             const int v = it - qk_items, head = v / chunks, c = v - head * chunks;
             float f[N];
             load(row + qw + kw + head * head_dim + c * N, f);
-            T* dst = v_cache + rdl_cache_offset(table, pos, page_size, ring_pages, n_kv_heads, head, head_dim);
+            T* dst = v_cache + rdl_cache_offset(page_list, pos, page_size, ring_pages, n_kv_heads, head, head_dim);
             store(dst + (VEC ? rdl_swizzled_chunk(r, c, chunks) * N : rdl_cache_col<T>(r, c, head_dim)), f);
             continue;
         }
@@ -462,29 +477,33 @@ __global__ void __launch_bounds__(256) rope_projnorm_cache_kernel(T* __restrict_
         const float inv = is_q ? inv_q : inv_k;
         const float* w = is_q ? wq + head * head_dim : wk + (head - n_heads) * head_dim;
         T* hrow = row + head * head_dim;
-        T* dst = (write && !is_q) ? k_cache + rdl_cache_offset(table, pos, page_size, ring_pages, n_kv_heads, head - n_heads, head_dim) : nullptr;
+        T* dst = (write && !is_q) ? k_cache + rdl_cache_offset(page_list, pos, page_size, ring_pages, n_kv_heads, head - n_heads, head_dim) : nullptr;
         auto place = [&](int c) { return VEC ? rdl_swizzled_chunk(r, c, chunks) * N : rdl_cache_col<T>(r, c, head_dim); };
         if (j < hc) {
             const int i0 = j * N;
-            float a[N], b[N];
+            float a[N], b[N], wa[N], wb[N], cs[N], sn[N];
             load(hrow + i0, a);
             load(hrow + i0 + half, b);
+            table(w + i0, wa);
+            table(w + i0 + half, wb);
+            table(cos_t + (long long)pos * half + i0, cs);
+            table(sin_t + (long long)pos * half + i0, sn);
 #pragma unroll
             for (int e = 0; e < N; ++e) {
-                const float u = a[e] * inv * w[i0 + e], v = b[e] * inv * w[i0 + half + e];
-                const float cs = cos_t[(long long)pos * half + i0 + e], sn = sin_t[(long long)pos * half + i0 + e];
-                a[e] = u * cs - v * sn;
-                b[e] = v * cs + u * sn;
+                const float u = a[e] * inv * wa[e], v = b[e] * inv * wb[e];
+                a[e] = u * cs[e] - v * sn[e];
+                b[e] = v * cs[e] + u * sn[e];
             }
             store(hrow + i0, a);
             store(hrow + i0 + half, b);
             if (dst) { store(dst + place(j), a); store(dst + place(j + hc), b); }
         } else {
             const int c = j + hc, i0 = c * N;
-            float a[N];
+            float a[N], wa[N];
             load(hrow + i0, a);
+            table(w + i0, wa);
 #pragma unroll
-            for (int e = 0; e < N; ++e) a[e] = a[e] * inv * w[i0 + e];
+            for (int e = 0; e < N; ++e) a[e] = a[e] * inv * wa[e];
             store(hrow + i0, a);
             if (dst) store(dst + place(c), a);
         }
@@ -514,10 +533,15 @@ extern "C" int rdl_rope_projnorm_cache(void* rows, long long row_stride, int dty
     const int per_chunk = dtype == RDL_BF16 ? 8 : 4;
     const int half = do_rope ? rotary_dim / 2 : 0;
     const bool vec = head_dim % per_chunk == 0 && half % per_chunk == 0 && row_stride % per_chunk == 0 &&
-                     (((uintptr_t)rows | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+                     (((uintptr_t)rows | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)wq | (uintptr_t)wk | (uintptr_t)cos_table |
+                       (uintptr_t)sin_table) & 15) == 0;
     cudaError_t e;
+    // bfloat16 steps of many tokens: small blocks, so that a multiprocessor holds many tokens (a block is a chain of a trip to
+    // memory, a barrier and a second trip; 8,192 tokens of 16 + 8 heads of 128 took 99 us with 256 threads, 69 with 128, 65 with
+    // 64).  Few tokens, and every 32-bit step (whose sums must not depend on the step's row count): 256 threads.
+    const int threads = dtype == RDL_BF16 && n_tokens >= 256 ? 64 : 256;
 #define RDL_PROJNORM(T, V)                                                                                                               \
-    e = rdl_launch(rope_projnorm_cache_kernel<T, V>, dim3(n_tokens), dim3(256), 0, st, (T*)rows, row_stride, n_heads, n_kv_heads, head_dim, \
+    e = rdl_launch(rope_projnorm_cache_kernel<T, V>, dim3(n_tokens), dim3(threads), 0, st, (T*)rows, row_stride, n_heads, n_kv_heads, head_dim, \
                    rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, wq, wk, eps, (float)q_count, (float)k_count, do_write,   \
                    (T*)k_cache, (T*)v_cache, tables, table_width, page_size, ring_pages, seq_end)
     if (dtype == RDL_BF16) { if (vec) RDL_PROJNORM(__nv_bfloat16, true); else RDL_PROJNORM(__nv_bfloat16, false); }

@@ -43,7 +43,9 @@ def _ti(a):
 # ---- each mechanism alone ----
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("sizes", [(3, 1, 12, 6, 0, 12), (6, 2, 16, 8, 5, 16), (4, 4, 64, 32, 0, 64), (5, 5, 24, 12, 3, 20), (2, 1, 8, 0, 0, 8)])
+@pytest.mark.parametrize("sizes", [(3, 1, 12, 6, 0, 12), (6, 2, 16, 8, 5, 16), (4, 4, 64, 32, 0, 64), (5, 5, 24, 12, 3, 20), (2, 1, 8, 0, 0, 8),
+                                   (40, 8, 256, 64, 0, 256), (20, 4, 256, 128, 0, 256), (16, 8, 128, 64, 0, 128), (24, 8, 128, 32, 0, 128),
+                                   (10, 2, 128, 64, 0, 128)])
 def test_projection_norm_rotation_and_cache_write(dtype, sizes):
     """The kernel between the q/k/v product and attention against the plain norm over the whole projections and the plain
     rotation: sizes that are whole numbers of 16-byte pieces and sizes that are not, rows wider than their heads, heads
@@ -110,6 +112,38 @@ def test_projection_norm_rotation_and_cache_write(dtype, sizes):
         assert torch.equal(k_ring[p, :, r], k_cache[pl, :, rl]) or r != rl
         if r == rl and (r & 7) == (rl & 7):
             assert torch.equal(v_ring[p, :, r], v_cache[pl, :, rl])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_projection_norm_with_many_tokens(dtype):
+    """Steps of many tokens take smaller blocks in bfloat16: 300 tokens at once against the same tokens eleven at a time and
+    against the plain norm and rotation; in 32-bit a token's values do not depend on the step's row count."""
+    from rust_deeplearning_b200.kernels import ops
+    from rust_deeplearning_b200.parts.position import Rotary
+    H, G, D, rot_n, T, eps = 6, 2, 64, 32, 300, 1e-4
+    rng = np.random.default_rng(7)
+    rows = _t(rng.normal(size=(T, (H + 2 * G) * D)), dtype)
+    wq, wk = _t(rng.normal(size=H * D) + 1.0, "float32"), _t(rng.normal(size=G * D) + 1.0, "float32")
+    part = Rotary(900.0, D, rot_n, 512, DEV, pairing="half")
+    pos = np.arange(5, 5 + T, dtype=np.int32)
+    kw = dict(wq=wq, wk=wk, eps=eps, q_count=H * D, k_count=G * D, cos=part.cos, sin=part.sin, rotary_dim=rot_n)
+    whole = rows.clone()
+    ops.rope_projnorm_cache(whole, H, G, D, tok_seq=_ti([0] * T), tok_pos=_ti(pos), **kw)
+    pieces = rows.clone()
+    for t0 in range(0, T, 11):
+        piece = pieces[t0:t0 + 11]
+        ops.rope_projnorm_cache(piece, H, G, D, tok_seq=_ti([0] * len(piece)), tok_pos=_ti(pos[t0:t0 + 11]), **kw)
+    if dtype == "float32":
+        assert torch.equal(whole, pieces)
+    else:
+        _close(whole, _back(pieces), dtype, "many tokens against few")
+    x, wq64, wk64 = _back(rows), _back(wq), _back(wk)
+    rot = {"base": 900.0, "dims": rot_n}
+    for t in (0, 137, 299):
+        qn = plain.rms_norm(x[t, :H * D], wq64, eps).reshape(H, D)
+        kn = plain.rms_norm(x[t, H * D:(H + G) * D], wk64, eps).reshape(G, D)
+        want = np.concatenate([plain.rotate(v, int(pos[t]), rot) for v in list(qn) + list(kn)] + [x[t, (H + G) * D:]])
+        _close(whole[t], want, dtype, f"token {t}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
