@@ -23,6 +23,9 @@ import sys
 
 
 
+MAX_LIVE = 256     # requests alive at once that the replay's cache has slots for
+
+
 def run(argv=None, stdin=None, stdout=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -30,7 +33,7 @@ def run(argv=None, stdin=None, stdout=None) -> int:
                     help="bfloat16: the serving kernels; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of the page size (64)")
+                    help="most tokens live requests hold at any time (padding not counted): the cache is sized for it")
     args = ap.parse_args(argv)
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
@@ -48,10 +51,15 @@ def run(argv=None, stdin=None, stdout=None) -> int:
     except (ConfigError, WeightError, SafetensorsError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 1
-    page = DEFAULT_PAGE_SIZE     # the unit requests' token counts are rounded up to
-    max_tokens = max(page, -(-args.max_tokens // page) * page)
-    engine = Engine(model, max_tokens=max_tokens, max_seqs=max_tokens // page,
-                    max_context=min(model.max_positions, max_tokens), page_size=page)
+    # The promise counts tokens; the cache hands out pages.  Every live request may leave its last page partly empty,
+    # and each holds at least one token, so there are at most --max-tokens of them (the engine is given up to MAX_LIVE
+    # slots): the cache gets the promised tokens plus a page's slack for every slot.
+    page = DEFAULT_PAGE_SIZE
+    promised = max(1, args.max_tokens)
+    longest = -(-promised // page) * page
+    n_slots = min(promised, MAX_LIVE)
+    engine = Engine(model, max_tokens=longest + n_slots * (page - 1), max_seqs=n_slots,
+                    max_context=min(model.max_positions, longest), page_size=page)
     slots = {}
     for line in stdin:
         line = line.strip()

@@ -518,6 +518,26 @@ def test_trace_replay_as_a_process(dtype, tmp_path):
     gh.assert_logits(read(4), wa[29:30], dtype, "step 4")
 
 
+def test_trace_replay_with_the_promise_counted_in_tokens(tmp_path):
+    """Seven short requests in one batch, then two tokens each, with --max-tokens set to the tokens they hold, padding not
+    counted (far fewer than seven pages' worth): the replay's cache has a slot and a page's slack for each of them."""
+    name, dtype = "GA", "float32"
+    seqs = [gh.prompt(name, 60 + i, n + 2, dtype) for i, n in enumerate((3, 1, 9, 20, 2, 5, 14))]
+    steps = [{"step": 0, "entries": [{"id": f"r{i}", "tokens": s[:-2], "want": [len(s) - 3]} for i, s in enumerate(seqs)], "end": []},
+             {"step": 1, "entries": [{"id": f"r{i}", "tokens": [s[-2]], "want": [0]} for i, s in enumerate(seqs)], "end": []},
+             {"step": 2, "entries": [{"id": f"r{i}", "tokens": [s[-1]], "want": [0]} for i, s in enumerate(seqs)], "end": [f"r{i}" for i in range(7)]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", gh.model_folder(name), "--dtype", dtype,
+                        "--out", str(tmp_path), "--max-tokens", str(sum(len(s) for s in seqs))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.split() == ["done", "0", "done", "1", "done", "2"], (r.stdout, r.stderr)
+    V = gh.vocab(name)
+    want = [gh.plain_logits(name, s) for s in seqs]
+    for n, at in ((0, -3), (1, -2), (2, -1)):
+        got = torch.tensor(np.fromfile(tmp_path / f"{n}.f32", dtype="<f4").reshape(-1, V))
+        gh.assert_logits(got, np.stack([w[at] for w in want]), dtype, f"step {n}")
+
+
 def test_command_line_generates_with_a_gasetar_folder(capsys):
     """The command line picks the architecture by config.json; its greedy tokens are the entry point's."""
     import io
