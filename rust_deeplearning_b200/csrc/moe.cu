@@ -461,7 +461,9 @@ extern "C" int rdl_moe_route(const void* x, int dtype, const float* w_router, co
     if (n_rows == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     // few rows: a block per expert with k split between its warps; many rows: 16 rows and 8 experts a block
-    const bool few = n_rows <= 64;
+    // (the two forms add a row's terms up in different orders: the 32-bit path, whose results must not depend on a step's
+    // row count, always takes the first)
+    const bool few = n_rows <= 64 || dtype == RDL_F32;
     const dim3 block(ROUTE_WARPS * 32);
     const dim3 grid = few ? dim3((n_rows + ROUTE_FEW_ROWS - 1) / ROUTE_FEW_ROWS, n_experts)
                           : dim3((n_rows + ROUTE_MANY_ROWS - 1) / ROUTE_MANY_ROWS, (n_experts + ROUTE_WARPS - 1) / ROUTE_WARPS);

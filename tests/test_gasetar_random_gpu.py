@@ -75,7 +75,7 @@ def draw(case: int):
     return rng, cfg, page, lengths
 
 
-@pytest.mark.parametrize("case", range(10))
+@pytest.mark.parametrize("case", range(16))
 def test_a_configuration_drawn_at_random(case):
     from rust_deeplearning_b200 import Engine, load_model, write_random_model
     from rust_deeplearning_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
