@@ -295,7 +295,7 @@ def gasetar_shape(width, heads, kv_heads, dim, window, latent_heads, latent_dim,
                   dense_ff, vocab, layers=4):
     """A Gasetar configuration of four layers: window attention with a dense feed-forward, latent attention with routed
     experts, and two window-attention layers with routed experts (each with a shared expert)."""
-    rot = {"base": 50000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    rot = {"base": 100000.0, "dims": dim * 3 // 4, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     attn = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "mask": {"size": window}, "rot": rot}
     latent = {"heads": latent_heads, "dim": latent_dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
               "scale": (latent_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
@@ -337,9 +337,9 @@ REVEPEL_SIZES = {
 GASETAR_SIZES = {
     # four layers each (window attention + dense, latent attention + experts, two of window attention + experts); Gemma 2 with
     # the same width, heads, key heads, head size and window, and a feed-forward as wide as the experts a token uses (top x ff + shared)
-    "w1024": (dict(width=1024, heads=8, kv_heads=4, dim=128, window=1024, latent_heads=8, latent_dim=64, rot_dim=64, vdim=128, kv_rank=192,
-                   experts=16, top=2, ff=768, shared_ff=512, dense_ff=2048, vocab=32000),
-              dict(width=1024, heads=8, kv_heads=4, head_dim=128, intermediate=2048, window=1024, layers=4, vocab=32000)),
+    "w1024": (dict(width=1024, heads=8, kv_heads=2, dim=128, window=1024, latent_heads=8, latent_dim=64, rot_dim=64, vdim=128, kv_rank=192,
+                   experts=32, top=4, ff=384, shared_ff=512, dense_ff=2048, vocab=32000),
+              dict(width=1024, heads=8, kv_heads=2, head_dim=128, intermediate=2048, window=1024, layers=4, vocab=32000)),
     "w2048": (dict(width=2048, heads=16, kv_heads=8, dim=128, window=4096, latent_heads=16, latent_dim=128, rot_dim=64, vdim=128, kv_rank=512,
                    experts=64, top=6, ff=1024, shared_ff=2304, dense_ff=8448, vocab=32000),
               dict(width=2048, heads=16, kv_heads=8, head_dim=128, intermediate=8448, window=4096, layers=4, vocab=32000)),

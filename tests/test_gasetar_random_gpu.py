@@ -22,10 +22,10 @@ MARGIN = {"float32": 1e-4, "bfloat16": 5e-2}
 
 def _rot(rng, limit):
     dims = int(rng.choice([d for d in (limit, limit // 2, 8, 6) if d % 2 == 0 and 2 <= d <= limit]))
-    rot = {"base": float(rng.choice([100.0, 10000.0, 500000.0])), "dims": dims}
+    rot = {"base": float(rng.choice([100.0, 10000.0, 250000.0])), "dims": dims}
     if rng.integers(0, 2):
         rot["scaling"] = {"factor": float(rng.choice([2.0, 8.0])), "low": 1.0, "high": float(rng.choice([4.0, 16.0])),
-                          "original": int(rng.choice([16, 64, 2048]))}
+                          "original": int(rng.choice([16, 64, 1024]))}
     return rot
 
 
@@ -66,10 +66,10 @@ def draw(case: int):
             layers.append({"type": "latent_attention", "mixer": m, "mlp": _mlp(rng)})
     cfg = {"architecture": "Gasetar", "width": int(rng.choice([48, 64, 72, 88, 136, 50])), "vocab": int(rng.integers(90, 400)),
            "norm": {"eps": float(rng.choice([1e-6, 1e-5, 1e-3]))}, "embedding": {"scale": float(rng.choice([1.0, 4.0, 9.5]))},
-           "residual_mult": float(rng.choice([1.0, 0.7, 0.25])), "logit_scale": float(rng.choice([1.0, 0.5, 1.7])),
+           "residual_mult": float(rng.choice([1.0, 0.8, 0.25])), "logit_scale": float(rng.choice([1.0, 0.4, 1.7])),
            "max_positions": 512, "layers": layers}
     if rng.integers(0, 2):
-        cfg["logit_softcap"] = float(rng.choice([10.0, 30.0]))
+        cfg["logit_softcap"] = float(rng.choice([10.0, 25.0]))
     page = int(rng.choice([16, 32, 64]))
     lengths = [int(v) for v in rng.integers(1, 90, size=int(rng.integers(1, 5)))]
     return rng, cfg, page, lengths
