@@ -102,13 +102,20 @@ def test_a_configuration_drawn_at_random(case):
             # rows up to a sequence's first close call of the router; what follows one is another computation
             safe = [int(np.argmax(m <= MARGIN[dtype])) if (m <= MARGIN[dtype]).any() else len(m) for m in least]
             eng = Engine(load_model(folder, dtype, "cuda:0"), max_tokens=2048, max_seqs=8, page_size=page)
+            # one tolerance for the whole case, from the largest logit of all its sequences (a step's few rows may hold small
+            # logits only, while the rounding of a bfloat16 model is that of its largest values)
+            largest = max(float(np.abs(w).max()) for w in want)
+            tol = 2e-5 * max(1.0, largest) if dtype == "float32" else 0.035 * largest + 1e-3
 
             def compare(got, rows, label):
                 """rows: (sequence, position) of each row of got"""
                 keep = [r for r, (i, p) in enumerate(rows) if p < safe[i]]
                 if keep:
-                    mh.assert_logits(got[torch.tensor(keep, device=got.device)], np.stack([want[rows[r][0]][rows[r][1]] for r in keep]),
-                                     dtype, f"{dtype}, {label}; {what}", bf16_fraction=0.03)
+                    g = got[torch.tensor(keep, device=got.device)].float().cpu().double().numpy()
+                    w = np.stack([want[rows[r][0]][rows[r][1]] for r in keep])
+                    assert np.isfinite(g).all(), f"{dtype}, {label}: non-finite logits; {what}"
+                    worst = float(np.abs(g - w).max())
+                    assert worst <= tol, f"{dtype}, {label}: max error {worst:.3e} > {tol:.3e} (row {int(np.abs(g - w).max(axis=1).argmax())} of {len(keep)}); {what}"
 
             slots = [eng.new_sequence() for _ in seqs]
             whole = eng.step(slots, seqs, "all").clone()
