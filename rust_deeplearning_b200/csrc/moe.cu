@@ -4,6 +4,7 @@
 //   z = W_r x,  s = softmax(z) over all experts (identity experts included), or s = sigmoid(z) expert by expert,
 //   choice = s + correction;  the `top` largest choices are taken (ties: the lower index),
 //   their weights are s itself (not renormalised).
+//   A third scoring: z = W_r x + b, the `top` largest z are taken and their weights are the softmax over those z alone.
 // An expert e < n_real is a gated feed-forward, y = W_down act(W_gate x, W_up x); an expert e >= n_real is
 // an identity expert whose output is x.  The row's result is sum_k weight_k y_k in the order of the choice.
 // Two further forms: experts of two matrices, y = W_down act(W_up x) (activation codes RDL_UNARY_*), and weights
